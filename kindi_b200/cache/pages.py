@@ -77,11 +77,13 @@ class PageMap:
     """The pages of one group of cache entries: per slot, the page of each block of ``PAGE`` positions.
 
     ``window`` None keeps all pages of a sequence; otherwise pages that lie wholly before the last ``window``
-    positions are given back as the sequence grows."""
+    positions are given back as the sequence grows, except the pages that hold any of the sequence's first
+    ``keep_first`` positions (queries go on reading those whatever their distance)."""
 
-    def __init__(self, n_pages: int, n_slots: int, window: Optional[int] = None):
+    def __init__(self, n_pages: int, n_slots: int, window: Optional[int] = None, keep_first: int = 0):
         self.pool = FreeList(n_pages, "cache page")
         self.window = window
+        self.keep_first = max(0, int(keep_first))
         self.rows: List[Dict[int, int]] = [dict() for _ in range(n_slots)]     # slot -> {block index: page}
         self.n_blocks: List[int] = [0] * n_slots                                # blocks mapped so far, per slot
         self.dirty: List[tuple] = []                                            # (slot, block, page or -1)
@@ -113,7 +115,7 @@ class PageMap:
         if first_needed <= 0:
             return
         row = self.rows[slot]
-        for b in [b for b in row if (b + 1) * PAGE <= first_needed]:
+        for b in [b for b in row if (b + 1) * PAGE <= first_needed and b * PAGE >= self.keep_first]:
             self.pool.give(row.pop(b))
             self.dirty.append((slot, b, -1))
 

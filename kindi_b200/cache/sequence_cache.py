@@ -65,7 +65,7 @@ class SequenceCache:
             pool = torch.zeros((len(entries), n_pool, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype,
                                device=self.device)
             table = torch.full((self.n_slots, self.n_pages), -1, dtype=torch.int32, device=self.device)
-            g = KVGroup(need, entries, pool, table, PageMap(n_pool, self.n_slots, need.window), n_pool)
+            g = KVGroup(need, entries, pool, table, PageMap(n_pool, self.n_slots, need.window, need.keep_first), n_pool)
             for j, e in enumerate(entries):
                 self._where[e] = (len(self.groups), j)
             self.groups.append(g)
@@ -74,12 +74,13 @@ class SequenceCache:
     @staticmethod
     def group_pages(need: KVNeed, n_pages: int, n_slots: int, max_step_tokens: Optional[int]) -> int:
         """pages of a group's pool. All keys: what the cache holds. A window: each sequence keeps the pages its window
-        touches (two more than the window fills: it starts and ends inside pages), and while a step runs also the
-        pages of its new tokens (each sequence's share again starts and ends inside pages); never more than a
-        full group"""
+        touches (two more than the window fills: it starts and ends inside pages) and the pages of the first positions
+        it keeps, and while a step runs also the pages of its new tokens (each sequence's share again starts and ends
+        inside pages); never more than a full group"""
         if need.window is None or max_step_tokens is None:
             return n_pages
-        return min(n_pages, n_slots * (pages_for(need.window) + 4) + pages_for(max_step_tokens))
+        return min(n_pages, n_slots * (pages_for(need.window) + 4 + pages_for(need.keep_first))
+                   + pages_for(max_step_tokens))
 
     @staticmethod
     def bytes_needed(needs: Sequence, max_tokens: int, n_slots: int, dtype: torch.dtype,

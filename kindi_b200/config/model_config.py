@@ -51,14 +51,17 @@ def read_config_json(model_dir: str) -> dict:
 
 
 def architecture_name(raw: Mapping[str, Any]) -> str:
-    """``architectures[0]``, else ``model_type``: the key of the architecture registry"""
+    """``architectures[0]``, else ``architecture``, else ``model_type``: the key of the architecture registry"""
     archs = raw.get("architectures")
     if isinstance(archs, (list, tuple)) and archs and isinstance(archs[0], str):
         return archs[0]
+    one = raw.get("architecture")
+    if isinstance(one, str):
+        return one
     mt = raw.get("model_type")
     if isinstance(mt, str):
         return mt
-    raise ConfigError("config.json: neither 'architectures' nor 'model_type' names the architecture")
+    raise ConfigError("config.json: neither 'architectures', 'architecture' nor 'model_type' names the architecture")
 
 
 class ConfigReader:

@@ -43,11 +43,14 @@ class LayerSpec:
 class ScheduleEntry:
     """One run of a layer. ``cache`` is the index of the cache entry (keys/values or state) this run owns;
     ``reads_cache_of`` names another schedule entry's cache entry whose keys and values this run attends to
-    instead of writing its own."""
+    instead of writing its own. ``add_embedding``: the embedding part's output of this step's rows is added to the
+    residual stream right before this run (a model that runs a stretch of layers several times feeds its input in
+    again at the start of every further pass)."""
 
     layer: int
     cache: int
     reads_cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

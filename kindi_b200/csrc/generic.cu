@@ -967,14 +967,15 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
 
 // ------------------------------------------------------------------------------------------------ attention
 // One warp per (row, query head). The row attends the keys of its sequence at positions lo..pos, lo = 0 or
-// pos - window + 1, read from the cache. Keys are taken in runs of 32 that start at multiples of 32 of the absolute
+// pos - window + 1, and with a window also the sequence's first keep_first positions (at their true positions), read
+// from the cache. Keys are taken in runs of 32 that start at multiples of 32 of the absolute
 // position (lane = position for the scores, lane = dimension for P V) with a running maximum and sum, so the order
 // of every sum depends on positions only: the same row gives the same bits whether it came in a prompt or alone.
 #define AG_MAX_HD 256
 template <typename T>
 __global__ void __launch_bounds__(128) k_attn_generic(const T* KB_STEP_DATA q, int ldq, T* __restrict__ out,
         int ldo, const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int Tn,
-        int nh, int group, int hd, float scale, int window, KbCacheView cv, int* status) {
+        int nh, int group, int hd, float scale, int window, int keep_first, KbCacheView cv, int* status) {
     __shared__ float qs[4][AG_MAX_HD];
     kb_pdl_launch();
     kb_pdl_wait();
@@ -995,9 +996,12 @@ __global__ void __launch_bounds__(128) k_attn_generic(const T* KB_STEP_DATA q, i
     float o[AG_MAX_HD / 32];
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; i++) o[i] = 0.0f;
-    for (int c0 = lo & ~31; c0 <= p_q; c0 += 32) {
+    // the runs that hold kept first positions and lie wholly before the window's first run, then the window's runs
+    const int c_lo = lo & ~31;
+    const int c_keep = min((keep_first + 31) & ~31, c_lo);
+    for (int c0 = c_keep > 0 ? 0 : c_lo; c0 <= p_q; c0 = (c0 + 32 == c_keep) ? c_lo : c0 + 32) {
         const int p = c0 + lane;
-        const bool live = p >= lo && p <= p_q;
+        const bool live = (p >= lo || p < keep_first) && p <= p_q;
         float sc = -1e30f;
         const T* vrow = nullptr;
         bool ok = live;
@@ -1044,18 +1048,20 @@ __global__ void __launch_bounds__(128) k_attn_generic(const T* KB_STEP_DATA q, i
 
 extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int ldo, const int* pos, const int* seq,
                                const int* slot, int T, int nh, int nkv, int hd, float scale, int window, void* pool,
-                               const int* table, int table_stride, int n_pages, int* status, cudaStream_t st) {
+                               const int* table, int table_stride, int n_pages, int* status, cudaStream_t st,
+                               int keep_first) {
     if (T <= 0) return 0;
     if (hd > AG_MAX_HD || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
+    if (window <= 0 || keep_first < 0) keep_first = 0;
     KbCacheView cv{pool, table, table_stride, n_pages, nkv, hd};
     long long items = (long long)T * nh;
     int grid = (int)((items + 3) / 4);
     if (dtype == KB_F32)
         kb_launch(k_attn_generic<float>, grid, 128, 0, st, (const float*)q, ldq, (float*)out, ldo, pos, seq, slot, T, nh,
-                                                   nh / nkv, hd, scale, window, cv, status);
+                                                   nh / nkv, hd, scale, window, keep_first, cv, status);
     else
         kb_launch(k_attn_generic<bf16>, grid, 128, 0, st, (const bf16*)q, ldq, (bf16*)out, ldo, pos, seq, slot, T, nh,
-                                                  nh / nkv, hd, scale, window, cv, status);
+                                                  nh / nkv, hd, scale, window, keep_first, cv, status);
     KB_LAUNCH_RET();
 }
 

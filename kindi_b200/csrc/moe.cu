@@ -1,0 +1,255 @@
+// Mixture of experts: the pick of each row's experts, the plan that sorts (row, pick) pairs by expert, and the two
+// grouped products of the general (fixed-order, 32-bit accumulate) path.
+//
+// k_moe_topk: z = logits + bias (32-bit); the `top` largest of a row's E values are taken one after the other (of
+// equal values the one with the lower index first); their weights are the softmax over the chosen values only.
+// Pair p = row * top + k names the k-th pick of a row.
+//
+// k_moe_plan (one block): counts the pairs of every expert, lays the experts' pairs one after another
+// (offs[e]..offs[e + 1]), lists the pairs in that order (perm) and cuts every expert's stretch into tiles of `tile`
+// rows (tile_e, tile_r0; n_tiles[0] tiles in all). Products then run over tiles; a tile belongs to one expert.
+// Which place a pair gets inside its expert's stretch depends on the order in which threads arrive, but a pair's
+// result does not depend on its place.
+//
+// k_moe_gemm: C[r][n] = sum_k A[r][k] * W[e][n][k] for every sorted row r of every tile, k in order with 32-bit fused
+// multiply-adds. Up form: A's row is the row of the pair's token (gathered through perm), the activation is applied
+// and C is the sorted intermediate. Down form: A is the sorted intermediate, the result is multiplied by the pair's
+// weight and written to plane k of the pair's token, so that the planes' sum in order is the weighted sum of the
+// chosen experts (the next norm adds the planes).
+#include "common.cuh"
+#include <math.h>
+
+#define KB_ACT_NONE 0
+#define KB_ACT_RELU2 1
+#define KB_ACT_SILU 2
+#define KB_ACT_GELU_TANH 3
+
+__device__ __forceinline__ float kb_act(float z, int act) {
+    switch (act) {
+        case KB_ACT_RELU2: {
+            const float r = fmaxf(z, 0.0f);
+            return r * r;
+        }
+        case KB_ACT_SILU: return z / (1.0f + expf(-z));
+        case KB_ACT_GELU_TANH:
+            return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        default: return z;
+    }
+}
+
+#define MOE_MAX_TOP 32
+
+__global__ void __launch_bounds__(128) k_moe_topk(const float* KB_STEP_DATA logits, int ldz,
+        const float* __restrict__ bias, int T, int E, int top, int* __restrict__ idx, float* __restrict__ wts) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * ldz;
+    int chosen[MOE_MAX_TOP];
+    float val[MOE_MAX_TOP];
+    for (int k = 0; k < top; k++) {
+        int best = -1;
+        float bv = 0.0f;
+        for (int e = 0; e < E; e++) {
+            bool taken = false;
+            for (int j = 0; j < k; j++) taken |= chosen[j] == e;
+            if (taken) continue;
+            const float v = z[e] + (bias ? bias[e] : 0.0f);
+            if (best < 0 || v > bv) {
+                best = e;
+                bv = v;
+            }
+        }
+        chosen[k] = best;
+        val[k] = bv;
+    }
+    float mx = val[0];
+    for (int k = 1; k < top; k++) mx = fmaxf(mx, val[k]);
+    float sum = 0.0f;
+    for (int k = 0; k < top; k++) {
+        val[k] = expf(val[k] - mx);
+        sum += val[k];
+    }
+    for (int k = 0; k < top; k++) {
+        idx[(size_t)t * top + k] = chosen[k];
+        wts[(size_t)t * top + k] = val[k] / sum;
+    }
+}
+
+extern "C" int kb_moe_topk(const float* logits, int ldz, const float* bias, int T, int E, int top, int* idx,
+                           float* wts, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (top < 1 || top > MOE_MAX_TOP || top > E) return (int)cudaErrorInvalidValue;
+    kb_launch(k_moe_topk, (T + 127) / 128, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts);
+    KB_LAUNCH_RET();
+}
+
+#define MOE_PLAN_THREADS 1024
+// shared: counts[E], cursor[E]
+__global__ void __launch_bounds__(MOE_PLAN_THREADS) k_moe_plan(const int* KB_STEP_DATA idx, int n_pairs, int E,
+        int tile, int* __restrict__ offs, int* __restrict__ perm, int* __restrict__ tile_e,
+        int* __restrict__ tile_r0, int* __restrict__ n_tiles) {
+    extern __shared__ int sh[];
+    int* counts = sh;
+    int* cursor = sh + E;
+    kb_pdl_launch();
+    for (int e = threadIdx.x; e < E; e += MOE_PLAN_THREADS) counts[e] = 0;
+    __syncthreads();
+    kb_pdl_wait();
+    for (int p = threadIdx.x; p < n_pairs; p += MOE_PLAN_THREADS) {
+        const int e = idx[p];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < E; e++) {
+            offs[e] = at;
+            cursor[e] = at;
+            for (int r = 0; r < counts[e]; r += tile) {
+                tile_e[nt] = e;
+                tile_r0[nt] = at + r;
+                nt++;
+            }
+            at += counts[e];
+        }
+        offs[E] = at;
+        n_tiles[0] = nt;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += MOE_PLAN_THREADS) {
+        const int e = idx[p];
+        if (e >= 0 && e < E) perm[atomicAdd(&cursor[e], 1)] = p;
+    }
+}
+
+extern "C" int kb_moe_plan(const int* idx, int n_pairs, int E, int tile, int* offs, int* perm, int* tile_e,
+                           int* tile_r0, int* n_tiles, cudaStream_t st) {
+    if (n_pairs <= 0) return 0;
+    if (E < 1 || E > 4096 || tile < 1) return (int)cudaErrorInvalidValue;
+    kb_launch(k_moe_plan, 1, MOE_PLAN_THREADS, (size_t)2 * E * sizeof(int), st, idx, n_pairs, E, tile, offs, perm,
+              tile_e, tile_r0, n_tiles);
+    KB_LAUNCH_RET();
+}
+
+#define MG_BM 64
+#define MG_BN 64
+#define MG_BK 32
+// UP: A rows are gathered (token of the pair), C = act(A W^T) at the sorted row. !UP: A rows are the sorted rows,
+// C = weight of the pair * (A W^T) at plane (pair % top), row (pair / top).
+template <typename TA, typename TW, typename TC, bool UP>
+__global__ void __launch_bounds__(256) k_moe_gemm(const TA* KB_STEP_DATA A, int lda, const TW* __restrict__ W,
+        TC* __restrict__ C, int ldc, size_t plane_stride, int N, int K, const int* KB_STEP_DATA n_tiles,
+        const int* KB_STEP_DATA tile_e, const int* KB_STEP_DATA tile_r0, const int* KB_STEP_DATA offs,
+        const int* KB_STEP_DATA perm, const float* KB_STEP_DATA wts, int top, int act) {
+    __shared__ float As[MG_BK][MG_BM + 1];
+    __shared__ float Ws[MG_BK][MG_BN + 1];
+    __shared__ int arow[MG_BM];                      // UP: the token's row of A; else the pair
+    kb_pdl_launch();
+    kb_pdl_wait();
+    if ((int)blockIdx.y >= n_tiles[0]) return;
+    const int e = tile_e[blockIdx.y], r0 = tile_r0[blockIdx.y];
+    const int r_end = min(offs[e + 1], r0 + MG_BM);
+    const int n0 = blockIdx.x * MG_BN;
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    if (tid < MG_BM) {
+        const int r = r0 + tid;
+        int v = -1;
+        if (r < r_end) v = UP ? perm[r] / top : perm[r];
+        arow[tid] = v;
+    }
+    __syncthreads();
+    const TW* We = W + (size_t)e * N * K;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    constexpr int PER = MG_BM * MG_BK / 256;
+    float ra[PER], rw[PER];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int el = tid + 256 * j, r = el / MG_BK, c = el % MG_BK;
+            const int n = n0 + r, k = k0 + c;
+            const bool live = r0 + r < r_end && k < K;
+            const size_t row = UP ? (size_t)(live ? arow[r] : 0) : (size_t)(r0 + r);
+            ra[j] = live ? kb_to_f<TA>(A[row * lda + k]) : 0.0f;
+            rw[j] = (n < N && k < K) ? kb_to_f<TW>(We[(size_t)n * K + k]) : 0.0f;
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += MG_BK) {
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            const int el = tid + 256 * j, r = el / MG_BK, c = el % MG_BK;
+            As[c][r] = ra[j];
+            Ws[c][r] = rw[j];
+        }
+        __syncthreads();
+        if (k0 + MG_BK < K) fetch(k0 + MG_BK);
+#pragma unroll
+        for (int k = 0; k < MG_BK; k++) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int rl = ty * 4 + i;
+        if (r0 + rl >= r_end) continue;
+        TC* crow;
+        float f = 1.0f;
+        if (UP) {
+            crow = C + (size_t)(r0 + rl) * ldc;
+        } else {
+            const int pair = arow[rl];
+            crow = C + (size_t)(pair % top) * plane_stride + (size_t)(pair / top) * ldc;
+            f = wts[pair];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) crow[n] = kb_from_f<TC>(UP ? kb_act(acc[i][j], act) : __fmul_rn(f, acc[i][j]));
+        }
+    }
+}
+
+// the tile size the plan has to be made with for these products
+extern "C" int kb_moe_gemm_tile() { return MG_BM; }
+
+extern "C" int kb_moe_gemm(const void* A, int adtype, int lda, const void* W, int wdtype, void* C, int cdtype,
+                           int ldc, long long plane_stride, int N, int K, int max_tiles, const int* n_tiles,
+                           const int* tile_e, const int* tile_r0, const int* offs, const int* perm,
+                           const float* wts, int top, int act, int up, cudaStream_t st) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    dim3 grid((N + MG_BN - 1) / MG_BN, max_tiles);
+#define KB_MG(TA, TW, TC, UP)                                                                                       \
+    kb_launch(k_moe_gemm<TA, TW, TC, UP>, grid, 256, 0, st, (const TA*)A, lda, (const TW*)W, (TC*)C, ldc,           \
+              (size_t)plane_stride, N, K, n_tiles, tile_e, tile_r0, offs, perm, wts, top, act)
+    if (up) {
+        if (adtype == KB_F32 && wdtype == KB_F32 && cdtype == KB_F32) KB_MG(float, float, float, true);
+        else if (adtype == KB_BF16 && wdtype == KB_BF16 && cdtype == KB_BF16) KB_MG(bf16, bf16, bf16, true);
+        else if (adtype == KB_BF16 && wdtype == KB_F32 && cdtype == KB_BF16) KB_MG(bf16, float, bf16, true);
+        else if (adtype == KB_F32 && wdtype == KB_BF16 && cdtype == KB_F32) KB_MG(float, bf16, float, true);
+        else return (int)cudaErrorInvalidValue;
+    } else {
+        if (cdtype != KB_F32) return (int)cudaErrorInvalidValue;
+        if (adtype == KB_F32 && wdtype == KB_F32) KB_MG(float, float, float, false);
+        else if (adtype == KB_BF16 && wdtype == KB_BF16) KB_MG(bf16, bf16, float, false);
+        else if (adtype == KB_BF16 && wdtype == KB_F32) KB_MG(bf16, float, float, false);
+        else if (adtype == KB_F32 && wdtype == KB_BF16) KB_MG(float, bf16, float, false);
+        else return (int)cudaErrorInvalidValue;
+    }
+#undef KB_MG
+    KB_LAUNCH_RET();
+}

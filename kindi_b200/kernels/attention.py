@@ -4,14 +4,16 @@ from __future__ import annotations
 from . import lib as K
 
 
-def attention(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages) -> None:
+def attention(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0) -> None:
     """``out`` = attention of the (already position-encoded) query rows ``q`` over their sequences' cached keys and
-    values, which include this step's"""
+    values, which include this step's: all positions up to the row's, or with ``window`` the last ``window`` of them
+    and the sequence's first ``keep_first``"""
     if ctx.fast:
         from . import fast
-        if fast.attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages):
+        if fast.attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first):
             return
-    K.attn_generic(q, out, ctx.pos, ctx.seq, ctx.slot, nh, nkv, hd, scale, window, pool, table, n_pages, ctx.status)
+    K.attn_generic(q, out, ctx.pos, ctx.seq, ctx.slot, nh, nkv, hd, scale, window, pool, table, n_pages, ctx.status,
+                   keep_first)
 
 
 def attention_from_planes(ctx, qkv, out, nh, nkv, hd, scale, window, rotation, pool, table, n_pages) -> bool:

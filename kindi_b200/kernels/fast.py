@@ -228,8 +228,10 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
     return True
 
 
-def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages) -> bool:
+def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0) -> bool:
     """the tensor-core attention kernel, where it takes the shape: head size 64 or 128, bf16, aligned rows"""
+    if keep_first and window:
+        return False
     if hd not in (64, 128) or q.dtype != torch.bfloat16 or q.stride(0) % 8 or q.data_ptr() % 16:
         return False
     g = nh // nkv
@@ -279,3 +281,8 @@ def attention_decode_rope(ctx, qkv, out, nh, nkv, hd, scale, window, inv_freq, r
     K.attn_decode_rope(qkv, inv_freq, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool,
                        store, table, n_pages, grid_x=splits, status=ctx.status)
     return True
+
+
+def moe_experts(ctx, y, idx, wts, wup, wdown, top, act):
+    """the experts' grouped products on the tensor cores, where a kernel takes the shape; None: not taken"""
+    return None

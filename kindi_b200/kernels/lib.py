@@ -40,7 +40,18 @@ _SIGS = {
                       c_void_p, c_void_p],
     "kb_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "kb_attn_generic": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                        c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+                        c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int],
+    "kb_add_layernorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int,
+                         c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "kb_residual_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p],
+    "kb_norm_rope_store": [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                           c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                           c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "kb_moe_topk": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "kb_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "kb_moe_gemm_tile": [],
+    "kb_moe_gemm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int,
+                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_longlong, c_void_p, c_void_p, c_int, c_int],
@@ -104,7 +115,8 @@ class KernelTiming:
 
     def __getattr__(self, name):                       # stands in for the library while timing is on
         fn = getattr(_lib, name)
-        if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits", "kb_rope_table_min_rows"):
+        if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits", "kb_rope_table_min_rows",
+                                                  "kb_moe_gemm_tile"):
             return fn
 
         def timed(*args):
@@ -258,6 +270,151 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor,
                                  n_out, T, E, 1 if write_back else 0, _p(status), _stream()), "add_rmsnorm")
 
 
+def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, b: torch.Tensor, eps: float,
+                  out: torch.Tensor, rows: Optional[torch.Tensor], write_back: bool, status: torch.Tensor) -> None:
+    """x (float32 [T, E]) + sum of delta ([S, T, E] float32) -> (v - mean) / sqrt(var + eps) * w + b -> out ([R, E]);
+    rows int32 or None"""
+    _need_cuda(x, delta, w, b, out, rows)
+    T, E = x.shape
+    n_out = out.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and w.shape == (E,) == b.shape
+    assert w.dtype == b.dtype and w.is_contiguous() and b.is_contiguous()
+    nd, stride = 0, 0
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and delta.shape[1:] == (T, E)
+        nd, stride = delta.shape[0], T * E
+    if rows is None:
+        assert n_out == T
+    else:
+        assert rows.dtype == torch.int32 and rows.numel() == n_out
+    if E > 51200:
+        raise KernelError("kindi_b200: layer norm supports a width up to 51200, found %d" % E)
+    _check(load().kb_add_layernorm(_p(x), _p(delta), nd, stride, _p(w), _p(b), dt(w), float(eps), _p(out), dt(out),
+                                   _p(rows), n_out, T, E, 1 if write_back else 0, _p(status), _stream()),
+           "add_layernorm")
+
+
+def residual_add(x: torch.Tensor, delta: Optional[torch.Tensor], extra: Optional[torch.Tensor]) -> None:
+    """x (float32 [T, E]) += sum of delta ([S, T, E] float32, in order) + extra ([T, E] float32); in place"""
+    _need_cuda(x, delta, extra)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    nd, stride = 0, 0
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and delta.shape[1:] == x.shape
+        nd, stride = delta.shape[0], x.numel()
+    if extra is not None:
+        assert extra.dtype == torch.float32 and extra.is_contiguous() and extra.shape == x.shape
+    _check(load().kb_residual_add(_p(x), _p(delta), nd, stride, _p(extra), x.numel(), _stream()), "residual_add")
+
+
+def norm_rope_store(qkv: torch.Tensor, qout: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor],
+                    eps: float, nq_true: int, nk_true: int, inv_freq: torch.Tensor, rot: int, pos, seq, slot, nh: int,
+                    nkv: int, nkv_store: int, hd: int, pool: Optional[torch.Tensor], table: torch.Tensor, n_pages: int,
+                    status: torch.Tensor) -> None:
+    """``rope_store`` with a norm in front: the query part and the key part of a row are each divided by their root
+    mean square over all their heads (``sqrt(sum / n_true + eps)``) and multiplied by the gains ``wq`` ([nh hd]) and
+    ``wk`` ([nkv hd]) before the rotation. qkv: rows or 32-bit planes of [q heads | k heads | v heads]"""
+    _need_cuda(qkv, qout, wq, wk, inv_freq, pool, table)
+    planes = qkv.shape[0] if qkv.dim() == 3 else 1
+    T = qkv.shape[-2]
+    assert qkv.stride(-1) == 1 and qkv.shape[-1] == (nh + 2 * nkv) * hd and qout.stride(1) == 1
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(1, rot // 2) and rot % 2 == 0 and rot <= hd
+    wd = F32
+    if wq is not None:
+        assert wq.dtype == wk.dtype and wq.numel() == nh * hd and wk.numel() == nkv * hd
+        assert wq.is_contiguous() and wk.is_contiguous()
+        wd = dt(wq)
+    if nkv_store:
+        assert pool is not None and pool.dtype == qout.dtype and pool.is_contiguous() and nkv_store == nkv
+    pstride = qkv.stride(0) if qkv.dim() == 3 else 0
+    rc = load().kb_norm_rope_store(_p(qkv), dt(qkv), planes, pstride, qkv.stride(-2), _p(qout), dt(qout),
+                                   qout.stride(0), _p(wq), _p(wk), wd, float(eps), int(nq_true), int(nk_true),
+                                   _p(inv_freq), rot, _p(pos), _p(seq), _p(slot), T, nh, nkv, nkv_store, hd,
+                                   _p(pool), _p(table), table.stride(0), n_pages, _p(status), _stream())
+    _check(rc, "norm_rope_store")
+
+
+ACT = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}
+
+
+def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """the ``top`` largest of each row of logits + bias (float32 [T, E]) and the softmax over those alone:
+    (idx int32 [T, top], weights float32 [T, top])"""
+    _need_cuda(logits, bias)
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous()
+    if not (1 <= top <= min(E, 32)):
+        raise KernelError("kindi_b200: a row picks 1 to 32 of its %d experts, found top = %d" % (E, top))
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _check(load().kb_moe_topk(_p(logits), logits.stride(0), _p(bias), T, E, top, _p(idx), _p(wts), _stream()),
+           "moe_topk")
+    return idx, wts
+
+
+class MoePlan:
+    """(row, pick) pairs sorted by expert and cut into tiles, all on the device (see ``csrc/moe.cu``)"""
+
+    __slots__ = ("n_pairs", "n_experts", "tile", "max_tiles", "offs", "perm", "tile_e", "tile_r0", "n_tiles")
+
+
+def moe_plan(idx: torch.Tensor, n_experts: int, tile: int) -> MoePlan:
+    _need_cuda(idx)
+    assert idx.dtype == torch.int32 and idx.is_contiguous()
+    n = idx.numel()
+    if n_experts > 4096:
+        raise KernelError("kindi_b200: up to 4096 experts, found %d" % n_experts)
+    pl = MoePlan()
+    pl.n_pairs, pl.n_experts, pl.tile = n, n_experts, tile
+    pl.max_tiles = -(-n // tile) + min(n_experts, n)
+    buf = torch.empty(n_experts + 1 + n + 2 * pl.max_tiles + 1, dtype=torch.int32, device=idx.device)
+    a = 0
+    pl.offs = buf[a:a + n_experts + 1]
+    a += n_experts + 1
+    pl.perm = buf[a:a + n]
+    a += n
+    pl.tile_e = buf[a:a + pl.max_tiles]
+    a += pl.max_tiles
+    pl.tile_r0 = buf[a:a + pl.max_tiles]
+    a += pl.max_tiles
+    pl.n_tiles = buf[a:a + 1]
+    _check(load().kb_moe_plan(_p(idx), n, n_experts, tile, _p(pl.offs), _p(pl.perm), _p(pl.tile_e), _p(pl.tile_r0),
+                              _p(pl.n_tiles), _stream()), "moe_plan")
+    return pl
+
+
+@functools.lru_cache(maxsize=1)
+def moe_gemm_tile() -> int:
+    return load().kb_moe_gemm_tile()
+
+
+def moe_gemm_up(y: torch.Tensor, w: torch.Tensor, plan: MoePlan, top: int, act: str, out: torch.Tensor) -> None:
+    """out[r] (sorted rows [n_pairs, F]) = act(y[token of pair perm[r]] @ w[expert of r]^T); w [E, F, K]"""
+    _need_cuda(y, w, out)
+    E, F, Kd = w.shape
+    assert y.stride(1) == 1 and y.shape[1] == Kd and w.is_contiguous() and out.shape == (plan.n_pairs, F)
+    assert out.stride(1) == 1 and plan.tile == moe_gemm_tile()
+    _check(load().kb_moe_gemm(_p(y), dt(y), y.stride(0), _p(w), dt(w), _p(out), dt(out), out.stride(0), 0, F, Kd,
+                              plan.max_tiles, _p(plan.n_tiles), _p(plan.tile_e), _p(plan.tile_r0), _p(plan.offs),
+                              _p(plan.perm), None, top, ACT[act], 1, _stream()), "moe_gemm_up")
+
+
+def moe_gemm_down(h: torch.Tensor, w: torch.Tensor, plan: MoePlan, wts: torch.Tensor, top: int,
+                  planes: torch.Tensor) -> None:
+    """planes[k][t] (float32 [top, T, N]) = wts[t][k] * (h[sorted row of pair (t, k)] @ w[its expert]^T); w [E, N, F]"""
+    _need_cuda(h, w, planes, wts)
+    E, N, F = w.shape
+    assert h.stride(1) == 1 and h.shape == (plan.n_pairs, F) and w.is_contiguous()
+    assert planes.dtype == torch.float32 and planes.is_contiguous() and planes.shape[0] == top and planes.shape[2] == N
+    assert wts.dtype == torch.float32 and wts.is_contiguous() and wts.numel() == plan.n_pairs
+    _check(load().kb_moe_gemm(_p(h), dt(h), h.stride(0), _p(w), dt(w), _p(planes), F32, N,
+                              planes.stride(0), N, F, plan.max_tiles, _p(plan.n_tiles), _p(plan.tile_e),
+                              _p(plan.tile_r0), _p(plan.offs), _p(plan.perm), _p(wts), top, 0, 0, _stream()),
+           "moe_gemm_down")
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M, N] = a[M, K] @ w[N, K]^T with 32-bit accumulation in a fixed order (no tensor cores)"""
     _need_cuda(a, w, out)
@@ -310,8 +467,10 @@ def rope_store(qkv: torch.Tensor, qout: torch.Tensor, inv_freq: torch.Tensor, ro
 
 
 def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nkv: int, hd: int, scale: float,
-                 window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, status: torch.Tensor) -> None:
-    """attention of each row of q ([T, >= nh hd], row stride free) over its sequence's cached keys and values"""
+                 window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, status: torch.Tensor,
+                 keep_first: int = 0) -> None:
+    """attention of each row of q ([T, >= nh hd], row stride free) over its sequence's cached keys and values: all
+    positions up to the row's, or with ``window`` the last ``window`` of them and the sequence's first ``keep_first``"""
     _need_cuda(q, out, pool, table)
     T = q.shape[0]
     if hd > 256:
@@ -319,7 +478,7 @@ def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nk
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == pool.dtype
     _check(load().kb_attn_generic(_p(q), dt(q), q.stride(0), _p(out), out.stride(0), _p(pos), _p(seq), _p(slot), T,
                                   nh, nkv, hd, float(scale), int(window), _p(pool), _p(table), table.stride(0),
-                                  n_pages, _p(status), _stream()), "attn_generic")
+                                  n_pages, _p(status), _stream(), int(keep_first)), "attn_generic")
 
 
 def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:

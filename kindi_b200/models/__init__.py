@@ -1,2 +1,3 @@
 """Architectures: each module maps its config.json to a ``ModelSpec`` and registers itself by name."""
 from . import nanbeige      # noqa: F401
+from . import vozinex       # noqa: F401

@@ -23,11 +23,13 @@ from ..config.spec import PartSpec
 @dataclass(frozen=True)
 class KVNeed:
     """keys and values of ``n_kv_heads`` x ``head_dim`` per position; ``window`` None keeps every position, else
-    only the last ``window`` positions are ever read (older pages are given back)."""
+    only the last ``window`` positions and the first ``keep_first`` positions of a sequence are ever read (pages
+    that hold neither are given back)."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -176,11 +178,13 @@ class PositionEncoding(Part):
         return None
 
     def encode_and_store(self, ctx: StepContext, qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int,
-                         n_kv_store: int, head_dim: int, pool, table, n_pages: int) -> None:
+                         n_kv_store: int, head_dim: int, pool, table, n_pages: int, qk_norm=None) -> None:
         """``qkv``: rows ``[T, (n_heads + 2 n_kv) head_dim]`` in the run dtype, or 32-bit planes ``[S, T, ...]`` whose
         sum they are. Writes the encoded query heads to ``q_out`` (``[T, >= n_heads head_dim]``; may be ``qkv``
         itself) and, when ``n_kv_store`` > 0, the encoded keys and the values of ``n_kv_store`` heads into ``pool``
-        at each row's position (``ctx.pos``) of its sequence's pages (``table``)"""
+        at each row's position (``ctx.pos``) of its sequence's pages (``table``). ``qk_norm`` (only passed by a mixer
+        that has one): ``(query gains, key gains, eps, query elements, key elements)`` of a root-mean-square norm
+        over the whole query projection and the whole key projection, applied before the encoding"""
         raise NotImplementedError
 
 

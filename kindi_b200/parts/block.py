@@ -3,7 +3,8 @@
 The adds are deferred: each norm first adds the branch that the part before it produced, so a block receives the
 previous block's pending branch and returns its own (the reference's arrangement, ``kindi/nanbeige.py:688-718``:
 ``nbq_add_rms_q8`` adds ``br`` into ``x`` before it normalises). Which mixer, feed-forward and norms a block has is
-given by its spec; the names of the sub-prefixes of its tensors are parameters too.
+given by its spec; the names of the sub-prefixes of its tensors are parameters too. A block whose spec gives no
+feed-forward (``None``) is ``x += mixer(norm1(x))`` alone and has no second norm.
 """
 from __future__ import annotations
 
@@ -26,9 +27,16 @@ class PreNormBlock(Block):
         return n
 
     @classmethod
+    def _roles(cls, spec: PartSpec):
+        """(role, sub-prefix) of the parts the block has: without a feed-forward there is no second norm either"""
+        has_ff = spec.get("feed_forward") is not None
+        return [(role, sub) for role, sub in cls._names(spec).items()
+                if has_ff or role not in ("norm2", "feed_forward")]
+
+    @classmethod
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
         out = {}
-        for role, sub in cls._names(spec).items():
+        for role, sub in cls._roles(spec):
             ps: PartSpec = spec[role]
             for suffix, shape in part_class(_CATEGORY[role], ps.kind).tensor_shapes(ps, width).items():
                 out[sub + suffix] = shape
@@ -37,7 +45,7 @@ class PreNormBlock(Block):
     @classmethod
     def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
         out = {}
-        for role, sub in cls._names(spec).items():
+        for role, sub in cls._roles(spec):
             ps: PartSpec = spec[role]
             for suffix, kind in part_class(_CATEGORY[role], ps.kind).tensor_init(ps, width).items():
                 out[sub + suffix] = kind
@@ -56,18 +64,25 @@ class PreNormBlock(Block):
             ps: PartSpec = spec[role]
             return part_class(_CATEGORY[role], ps.kind)(ps, width, weights.sub(names[role]), dtype=dtype,
                                                         device=device)
-        self.norm1, self.mixer, self.norm2, self.feed_forward = (make(r) for r in
-                                                                 ("norm1", "mixer", "norm2", "feed_forward"))
-        self.graph_safe = all(p.graph_safe for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
+        self.norm1, self.mixer = make("norm1"), make("mixer")
+        self.norm2 = self.feed_forward = None
+        if spec.get("feed_forward") is not None:
+            self.norm2, self.feed_forward = make("norm2"), make("feed_forward")
+        self.graph_safe = all(p.graph_safe for p in self._parts())
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
 
     def forward(self, ctx: StepContext, x, pending: Optional[Branch]) -> Optional[Branch]:
         y = self.norm1.add_norm(ctx, x, pending)
         pending = self.mixer.forward(ctx, y)
+        if self.feed_forward is None:
+            return pending
         y = self.norm2.add_norm(ctx, x, pending)
         return self.feed_forward.forward(ctx, y)
 
     def bytes_read(self) -> int:
-        return sum(p.bytes_read() for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
+        return sum(p.bytes_read() for p in self._parts())
 
 
 register_part("block", "prenorm", PreNormBlock)

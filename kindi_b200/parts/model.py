@@ -12,6 +12,7 @@ import torch
 
 from ..config.registry import part_class
 from ..config.spec import ModelSpec
+from ..kernels import lib as K
 from .base import Branch, StepContext, WeightView
 
 
@@ -74,8 +75,13 @@ class DecoderModel:
         """run the step's tokens through every scheduled layer (keys, values and state are stored on the way);
         returns 32-bit logits ``[len(rows), vocab]`` of the listed rows, or None when no row is wanted"""
         x = self.embedding.forward(ctx)
+        # a schedule that feeds the embedding output in again needs it as it was: the norms update x in place
+        x0 = self.embedding.forward(ctx) if any(e.add_embedding for e in self.spec.schedule) else None
         pending: Optional[Branch] = None
         for entry in self.spec.schedule:
+            if entry.add_embedding:
+                K.residual_add(x, None if pending is None else pending.parts, x0)
+                pending = None
             ctx.entry = entry
             pending = self.blocks[entry.layer].forward(ctx, x, pending)
         ctx.entry = None

@@ -1,4 +1,4 @@
-"""RMS norm with the residual add fused in front of it.
+"""Norms with the residual add fused in front of them: RMS norm, and layer norm with weight and bias.
 
 ``v = x + pending branch`` (written back to the 32-bit residual), ``y = (rsqrt(mean(v^2) + eps) * v) * w`` with the
 sum of squares, the scale and both products in 32-bit - the reference's ``nbq_add_rms_q8`` (``kindi/nbq.cu:412-432``)
@@ -42,4 +42,43 @@ class RMSNorm(Norm):
         return self.weight.numel() * self.weight.element_size()
 
 
+class LayerNorm(Norm):
+    """``v = x + pending branch`` (written back), ``y = (v - mean(v)) / sqrt(var(v) + eps) * w + b`` with the variance
+    the mean of the squared deviations, all in 32-bit. ``eps`` and the tensors' suffixes (``weight``, ``bias``) are
+    parameters of the part."""
+
+    @classmethod
+    def _names(cls, spec: PartSpec):
+        return spec.get("weight", "weight"), spec.get("bias", "bias")
+
+    @classmethod
+    def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
+        w, b = cls._names(spec)
+        return {w: (width,), b: (width,)}
+
+    @classmethod
+    def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
+        w, b = cls._names(spec)
+        return {w: "gain", b: "zero"}
+
+    def __init__(self, spec, width, weights: WeightView, *, dtype, device):
+        super().__init__(spec, width, weights, dtype=dtype, device=device)
+        self.eps = float(spec["eps"])
+        w, b = self._names(spec)
+        self.weight, self.bias = weights(w), weights(b)
+        if self.weight.dtype != self.bias.dtype:
+            raise ValueError("weight and bias of the norm %s are stored in different dtypes" % weights.prefix)
+
+    def add_norm(self, ctx: StepContext, x, pending: Optional[Branch], rows=None):
+        n_out = x.shape[0] if rows is None else rows.numel()
+        y = torch.empty((n_out, self.width), dtype=self.dtype, device=x.device)
+        K.add_layernorm(x, None if pending is None else pending.parts, self.weight, self.bias, self.eps, y, rows,
+                        write_back=rows is None and pending is not None, status=ctx.status)
+        return y
+
+    def bytes_read(self) -> int:
+        return 2 * self.weight.numel() * self.weight.element_size()
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)

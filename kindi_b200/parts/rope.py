@@ -28,7 +28,16 @@ class RotationEncoding(PositionEncoding):
     def rotation(self):
         return self.inv_freq, self.rotary_dim
 
-    def encode_and_store(self, ctx, qkv, q_out, n_heads, n_kv_store, head_dim, pool, table, n_pages) -> None:
+    def encode_and_store(self, ctx, qkv, q_out, n_heads, n_kv_store, head_dim, pool, table, n_pages,
+                         qk_norm=None) -> None:
+        if qk_norm is not None:
+            # a norm over the whole query and key projections comes before the rotation: one kernel does both
+            wq, wk, eps, nq_true, nk_true = qk_norm
+            n_kv = wk.numel() // head_dim
+            K.norm_rope_store(qkv, q_out, wq, wk, eps, nq_true, nk_true, self.inv_freq, self.rotary_dim, ctx.pos,
+                              ctx.seq, ctx.slot, n_heads, n_kv, n_kv_store, head_dim, pool if n_kv_store else None,
+                              table, n_pages, ctx.status)
+            return
         angles = None
         if self.angles_key is not None and ctx.T >= K.rope_table_min_rows() and self.rotary_dim >= 16:
             angles = ctx.scratch.get(self.angles_key)
