@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         const bf16* KB_STEP_DATA q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
         float* __restrict__ part_ml, const int* __restrict__ slot, const int* __restrict__ q_start,
         const int* __restrict__ kv_len, int nh, int nkv, int G, float scale_log2e, int window,
-        const int* __restrict__ table, int table_stride, int n_pages, int* status, AtRopeIn rp) {
+        const int* __restrict__ table, int table_stride, int n_pages, int* status, AtRopeIn rp, int keep_first) {
     static_assert(!ROPE || DEC, "rotation inside the kernel: decode form only");
     constexpr int AT_STAGES = DEC ? 3 : 2;      // pages in flight (two CTAs fit an SM in both forms)
     constexpr int KT = HD / 16;                 // k-steps of Q K^T
@@ -126,14 +126,19 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
     const int qs0 = q_start[b], qlen = q_start[b + 1] - qs0, kvl = kv_len[b];
     const int pos0 = kvl - qlen;                 // position of the sequence's first row of this step
     const int n_rows = qlen * G;
-    int row0, pg_lo, pg_hi;                      // the CTA's first row; its pages [pg_lo, pg_hi]
+    // The pages a CTA reads are a stretch [it_lo, it_lo + n_iter) of the list "pages that hold kept first positions
+    // and lie before the window's first page, then the window's pages [pg_first, ...]": entry i is page pgi(i).
+    int row0, pg_first, n_keep, it_lo, n_iter;
     if (DEC) {
         row0 = 0;
         const int lo = (window > 0 && kvl - window > 0) ? kvl - window : 0;       // row position is kvl - 1
-        const int first = lo / KB_PAGE, last = (kvl - 1) / KB_PAGE;
-        const int per = (last - first + (int)gridDim.x) / (int)gridDim.x;        // ceil(pages / splits)
-        pg_lo = first + (int)blockIdx.x * per;
-        pg_hi = min(last, pg_lo + per - 1);
+        const int last = (kvl - 1) / KB_PAGE;
+        pg_first = lo / KB_PAGE;
+        n_keep = min((keep_first + KB_PAGE - 1) / KB_PAGE, pg_first);
+        const int total = n_keep + last - pg_first + 1;
+        const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;           // ceil(pages / splits)
+        it_lo = (int)blockIdx.x * per;
+        n_iter = min(total, it_lo + per) - it_lo;                                // may be <= 0 for an empty split
     } else {
         const int n_tiles = (n_rows + AT_ROWS - 1) / AT_ROWS;
         if ((int)blockIdx.x >= n_tiles) return;
@@ -141,10 +146,12 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         const int last_row = min(n_rows, row0 + AT_ROWS) - 1;
         const int p_first = pos0 + row0 / G, p_last = pos0 + last_row / G;
         const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
-        pg_lo = lo / KB_PAGE;
-        pg_hi = p_last / KB_PAGE;
+        pg_first = lo / KB_PAGE;
+        n_keep = min((keep_first + KB_PAGE - 1) / KB_PAGE, pg_first);
+        it_lo = 0;
+        n_iter = n_keep + p_last / KB_PAGE - pg_first + 1;
     }
-    const int n_iter = pg_hi - pg_lo + 1;        // may be <= 0 for an empty decode split
+    auto pgi = [&](int i) { return it_lo + i < n_keep ? it_lo + i : pg_first + it_lo + i - n_keep; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < AT_STAGES; s++) {
@@ -171,12 +178,12 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
                 const int s = i % AT_STAGES;
                 const uint32_t ph = (uint32_t)(i / AT_STAGES) & 1u;
                 // (with rotation and a key of its own the newest row is patched in shared memory, so its page may come early too)
-                if (DEC && !waited && (i >= AT_EARLY || (pg_lo + i == (kvl - 1) / KB_PAGE && !(ROPE && rp.pool)))) {
+                if (DEC && !waited && (i >= AT_EARLY || (pgi(i) == (kvl - 1) / KB_PAGE && !(ROPE && rp.pool)))) {
                     kb_pdl_wait();
                     waited = true;
                 }
                 if (!mbar_wait(bar_empty + s * 8, ph ^ 1u, status)) break;
-                int page = trow[pg_lo + i];
+                int page = trow[pgi(i)];
                 if (page < 0 || page >= n_pages) {
                     if (!waited) kb_pdl_wait();              // the status word is shared with earlier kernels
                     waited = true;
@@ -204,7 +211,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         const int tid = threadIdx.x;                 // 0..127 here: the consumer threads
         float knew_lo[PPL], knew_hi[PPL], vnew[2][PPL];
         const int p_new = kvl - 1;
-        const bool owns_new = ROPE && rp.pool != nullptr && p_new / KB_PAGE >= pg_lo && p_new / KB_PAGE <= pg_hi &&
+        const bool owns_new = ROPE && rp.pool != nullptr && n_iter > 0 && p_new / KB_PAGE == pgi(n_iter - 1) &&
                               warp == (p_new % KB_PAGE) / 16;
         if (ROPE) {
             // Queries: pair e = tid + 128 k is (row e / HALF, pair e % HALF of the head) and 128 is a multiple of HALF,
@@ -317,7 +324,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
             const int s = i % AT_STAGES;
             const uint32_t ph = (uint32_t)(i / AT_STAGES) & 1u;
             if (!mbar_wait(bar_full + s * 8, ph, status)) break;
-            if (ROPE && owns_new && pg_lo + i == p_new / KB_PAGE) {
+            if (ROPE && owns_new && pgi(i) == p_new / KB_PAGE) {
                 // the newest position's row of this page: the values computed above, over what the load brought
                 uint8_t* kt8 = smem + s * STAGE_BYTES;
                 const int row = p_new % KB_PAGE;
@@ -335,7 +342,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
                 }
                 __syncwarp();
             }
-            const int key0 = (pg_lo + i) * KB_PAGE + kw0;           // absolute position of the warp's first key
+            const int key0 = pgi(i) * KB_PAGE + kw0;           // absolute position of the warp's first key
             if (key0 <= wlast) {
                 const uint32_t kt = sbase + s * STAGE_BYTES, vt = kt + TILE_BYTES;
                 float sc[NT][4];
@@ -357,10 +364,10 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
 #pragma unroll
                 for (int n = 0; n < NT; n++) {
                     const int p = key0 + n * 8 + (lane & 3) * 2;
-                    sc[n][0] = (p <= pa && p >= la) ? sc[n][0] * scale_log2e : -INFINITY;
-                    sc[n][1] = (p + 1 <= pa && p + 1 >= la) ? sc[n][1] * scale_log2e : -INFINITY;
-                    sc[n][2] = (p <= pb && p >= lb) ? sc[n][2] * scale_log2e : -INFINITY;
-                    sc[n][3] = (p + 1 <= pb && p + 1 >= lb) ? sc[n][3] * scale_log2e : -INFINITY;
+                    sc[n][0] = (p <= pa && (p >= la || p < keep_first)) ? sc[n][0] * scale_log2e : -INFINITY;
+                    sc[n][1] = (p + 1 <= pa && (p + 1 >= la || p + 1 < keep_first)) ? sc[n][1] * scale_log2e : -INFINITY;
+                    sc[n][2] = (p <= pb && (p >= lb || p < keep_first)) ? sc[n][2] * scale_log2e : -INFINITY;
+                    sc[n][3] = (p + 1 <= pb && (p + 1 >= lb || p + 1 < keep_first)) ? sc[n][3] * scale_log2e : -INFINITY;
                     mxa = fmaxf(mxa, fmaxf(sc[n][0], sc[n][1]));
                     mxb = fmaxf(mxb, fmaxf(sc[n][2], sc[n][3]));
                 }
@@ -543,7 +550,7 @@ template <int HD, bool DEC, bool ROPE = false>
 static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, float* part_o,
                        float* part_ml, const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv,
                        float scale, int window, const int* table, int table_stride, int n_pages, int grid_x,
-                       int* status, cudaStream_t st, AtRopeIn rp = AtRopeIn()) {
+                       int* status, cudaStream_t st, AtRopeIn rp = AtRopeIn(), int keep_first = 0) {
     auto kern = k_attn_mma<HD, DEC, ROPE>;
     int sm = attn_smem_bytes<HD, DEC>();
     constexpr int ALONE = 118 * 1024;   // more than half of an SM's shared memory: a CTA that asks for it has the SM to itself
@@ -559,7 +566,7 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
     dim3 grid(grid_x, nkv, B);
     kb_launch(kern, grid, AT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, slot, q_start,
                                        kv_len, nh, nkv, nh / nkv, scale * 1.4426950408889634f, window, table,
-                                       table_stride, n_pages, status, rp);
+                                       table_stride, n_pages, status, rp, keep_first);
     return (int)cudaGetLastError();
 }
 
@@ -569,8 +576,9 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
 extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* part_o, float* part_ml,
                            const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv, int hd,
                            float scale, int window, void* pool, const int* table, int table_stride, int n_pages,
-                           int decode, int grid_x, int* status, cudaStream_t st) {
+                           int decode, int grid_x, int* status, cudaStream_t st, int keep_first) {
     if (B <= 0 || grid_x <= 0) return 0;
+    if (window <= 0 || keep_first < 0) keep_first = 0;
     if (decode && grid_x > 64) return (int)cudaErrorInvalidValue;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
     if (decode && nh / nkv > 16) return (int)cudaErrorInvalidValue;
@@ -580,7 +588,7 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
     if (rc) return rc;
 #define AT_GO(HD, DEC)                                                                                          \
     rc = launch_attn<HD, DEC>(map, q, ldq, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv, scale, \
-                              window, table, table_stride, n_pages, grid_x, status, st)
+                              window, table, table_stride, n_pages, grid_x, status, st, AtRopeIn(), keep_first)
     if (hd == 128) {
         if (decode) AT_GO(128, true); else AT_GO(128, false);
     } else {
@@ -684,5 +692,5 @@ extern "C" int kb_attn_decode_static(const void* q, int ldq, void* out, int ldo,
     float* part_o = base_of_device[dev];
     float* part_ml = part_o + (size_t)B * nh * n_splits * hd;
     return kb_attn_mma(q, ldq, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv, hd, scale, window, pool,
-                       table, table_stride, n_pages, 1, n_splits, status, st);
+                       table, table_stride, n_pages, 1, n_splits, status, st, 0);
 }

@@ -87,7 +87,7 @@ template <int FT_HD>
 __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
         const bf16* KB_STEP_DATA q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
-        const int* __restrict__ table, int table_stride, int n_pages, int* status) {
+        const int* __restrict__ table, int table_stride, int n_pages, int* status, int keep_first) {
     constexpr int FT_TILE_BYTES = 64 * FT_HD * 2, FT_STAGE_BYTES = 2 * FT_TILE_BYTES, FT_Q_BYTES = 128 * FT_HD * 2;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -136,7 +136,11 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
     const int p_first = pos0 + tok0, p_last = pos0 + tok0 + ntok - 1;
     const int lo_cta = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
     const int pg_lo = lo_cta / KB_PAGE, pg_hi = p_last / KB_PAGE;
-    const int n_iter = active ? pg_hi - pg_lo + 1 : 0;
+    // with a window, the pages that hold the sequence's kept first positions and lie before the window's first page
+    // come first; iteration i reads page pgi(i)
+    const int n_keep = min((keep_first + KB_PAGE - 1) / KB_PAGE, pg_lo);
+    const int n_iter = active ? n_keep + pg_hi - pg_lo + 1 : 0;
+    auto pgi = [&](int i) { return i < n_keep ? i : pg_lo + i - n_keep; };
 
     tc_fence_before();
     __syncthreads();                                 // the barriers and the tensor memory's address are there
@@ -175,7 +179,7 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             const int* trow = table + (size_t)slot[b] * table_stride;
             // two streams, keys and values, each held back only by its own tiles; one thread polls both
             auto page_of = [&](int i) {
-                int page = trow[pg_lo + i];
+                int page = trow[pgi(i)];
                 if (page < 0 || page >= n_pages) {
                     atomicOr(status, KB_ST_BAD_PAGE);
                     page = 0;
@@ -294,10 +298,10 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
             tc_fence_before();
             __syncwarp();
             // scale, mask, row maximum
-            const int key0 = (pg_lo + j) * KB_PAGE;
+            const int key0 = pgi(j) * KB_PAGE;
             // four independent running maxima (one long dependent chain would leave the few resident warps idle)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            if (key0 + 63 <= p_row && key0 >= lo_row) {
+            if (key0 + 63 <= p_row && (key0 >= lo_row || key0 + 63 < keep_first)) {
                 // the whole page lies inside this row's span (all pages but the last one or two): no masks
 #pragma unroll
                 for (int c = 0; c < 64; c += 8) {
@@ -309,7 +313,7 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
 #pragma unroll
                 for (int c = 0; c < 64; c++) {
                     const int p = key0 + c;
-                    const float s = (p <= p_row && p >= lo_row) ? __uint_as_float(sv[c]) : -INFINITY;
+                    const float s = (p <= p_row && (p >= lo_row || p < keep_first)) ? __uint_as_float(sv[c]) : -INFINITY;
                     sv[c] = __float_as_uint(s);
                     mx4[c & 3] = fmaxf(mx4[c & 3], s);
                 }
@@ -427,7 +431,8 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
 template <int HD>
 static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, const int* slot,
                           const int* q_start, const int* kv_len, int B, int nh, int nkv, float scale, int window,
-                          const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st) {
+                          const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st,
+                          int keep_first) {
     // tiles (Q and two stages of keys and values: 96 KB at head size 128) + barriers + what aligning the base to 1024
     // can cost when it is aligned to 128: two CTAs fit an SM
     const int sm = 128 * HD * 2 + FT_STAGES * 2 * 64 * HD * 2 + 256 + 768;
@@ -439,15 +444,17 @@ static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* 
     dim3 grid(nkv, grid_x, B);
     cudaError_t e = kb_launch(k_attn_tc<HD>, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot,
                               q_start, kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table, table_stride,
-                              n_pages, status);
+                              n_pages, status, keep_first);
     return (int)e;
 }
 
 // grid_x = the most tiles of a sequence: ceil(longest q_len / (128 / G)) with G = nh / nkv <= 128; head size 64 or 128
 extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int* slot, const int* q_start,
                           const int* kv_len, int B, int nh, int nkv, int hd, float scale, int window, void* pool,
-                          const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st) {
+                          const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st,
+                          int keep_first) {
     if (B <= 0 || grid_x <= 0) return 0;
+    if (window <= 0 || keep_first < 0) keep_first = 0;
     if (grid_x > 65535 || B > 65535) return (int)cudaErrorInvalidValue;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 128) return (int)cudaErrorInvalidValue;
     if ((ldq % 8) || (ldo % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return (int)cudaErrorInvalidValue;
@@ -456,7 +463,7 @@ extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int*
     if (rc) return rc;
     if (hd == 128)
         return launch_attn_tc<128>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
-                                   table_stride, n_pages, grid_x, status, st);
+                                   table_stride, n_pages, grid_x, status, st, keep_first);
     return launch_attn_tc<64>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
-                              table_stride, n_pages, grid_x, status, st);
+                              table_stride, n_pages, grid_x, status, st, keep_first);
 }

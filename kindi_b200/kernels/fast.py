@@ -230,24 +230,22 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
 
 def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0) -> bool:
     """the tensor-core attention kernel, where it takes the shape: head size 64 or 128, bf16, aligned rows"""
-    if keep_first and window:
-        return False
     if hd not in (64, 128) or q.dtype != torch.bfloat16 or q.stride(0) % 8 or q.data_ptr() % 16:
         return False
     g = nh // nkv
     if ctx.decode and g <= 16:
         splits = decode_splits(ctx, nkv)
         K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table,
-                   n_pages, decode=True, grid_x=splits, status=ctx.status)
+                   n_pages, decode=True, grid_x=splits, status=ctx.status, keep_first=keep_first)
         return True
     # (in a recording ctx.max_q is the most rows a sequence can bring: the grid then has tiles to spare, which leave)
     if g <= 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
         # prompt-sized steps: the tcgen05 kernel (S and O in tensor memory)
         K.attn_tc(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,
-                  grid_x=-(-ctx.max_q // (128 // g)), status=ctx.status)
+                  grid_x=-(-ctx.max_q // (128 // g)), status=ctx.status, keep_first=keep_first)
         return True
     K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,
-               decode=False, grid_x=-(-ctx.max_q * g // 64), status=ctx.status)
+               decode=False, grid_x=-(-ctx.max_q * g // 64), status=ctx.status, keep_first=keep_first)
     return True
 
 

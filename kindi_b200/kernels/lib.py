@@ -62,12 +62,13 @@ _SIGS = {
     "kb_gemm_swiglu_decode": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                               c_void_p, c_void_p, c_void_p],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                    c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                    c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                    c_int],
     "kb_attn_decode_rope": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                             c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_attn_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
     "kb_sample": [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
                   c_void_p],
     "kb_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_float, c_void_p],
@@ -569,9 +570,10 @@ def gemm_tc_splits(K: int, wanted: int) -> int:
 
 def attn_mma(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
              scale: float, window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, decode: bool,
-             grid_x: int, status: torch.Tensor) -> None:
+             grid_x: int, status: torch.Tensor, keep_first: int = 0) -> None:
     """tensor-core attention over the cache (bf16, head size 64 or 128). decode: one row per sequence, grid_x =
-    position splits; else grid_x = ceil(most rows of a sequence * (nh / nkv) / 64)"""
+    position splits; else grid_x = ceil(most rows of a sequence * (nh / nkv) / 64). ``keep_first``: with a window,
+    the sequence's first positions that stay visible"""
     _need_cuda(q, out, pool, table)
     assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert pool.is_contiguous()
@@ -581,8 +583,8 @@ def attn_mma(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, 
         part_ml = torch.empty((B, nh, grid_x, 2), dtype=torch.float32, device=q.device)
     _check(load().kb_attn_mma(_p(q), q.stride(0), _p(out), out.stride(0), _p(part_o), _p(part_ml), _p(slot),
                               _p(q_start), _p(kv_len), B, nh, nkv, hd, float(scale), int(window), _p(pool), _p(table),
-                              table.stride(0), n_pages, 1 if decode else 0, grid_x, _p(status), _stream()),
-           "attn_mma")
+                              table.stride(0), n_pages, 1 if decode else 0, grid_x, _p(status), _stream(),
+                              int(keep_first)), "attn_mma")
     if decode and grid_x > 1:
         add_launches(1)         # the merge of the position splits
 
@@ -611,12 +613,12 @@ def attn_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tenso
 
 def attn_tc(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
             scale: float, window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, grid_x: int,
-            status: torch.Tensor) -> None:
+            status: torch.Tensor, keep_first: int = 0) -> None:
     """tcgen05 attention for prompt-sized steps (bf16, head size 64 or 128): grid_x = ceil(most rows of a sequence /
-    (128 // (nh / nkv)))"""
+    (128 // (nh / nkv))). ``keep_first``: with a window, the sequence's first positions that stay visible"""
     _need_cuda(q, out, pool, table)
     assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert pool.is_contiguous() and hd in (64, 128)
     _check(load().kb_attn_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(slot), _p(q_start), _p(kv_len), B, nh, nkv,
                              hd, float(scale), int(window), _p(pool), _p(table), table.stride(0), n_pages, grid_x,
-                             _p(status), _stream()), "attn_tc")
+                             _p(status), _stream(), int(keep_first)), "attn_tc")
