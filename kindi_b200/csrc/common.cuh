@@ -55,6 +55,24 @@ __device__ __forceinline__ size_t kb_kv_offset(const KbCacheView& c, int page, i
     return ((((size_t)page * 2 + kv) * c.n_kv + head) * KB_PAGE + p_in_page) * (size_t)c.head_dim;
 }
 
+// activations of a feed-forward that takes its activation as a parameter
+#define KB_ACT_NONE 0
+#define KB_ACT_RELU2 1
+#define KB_ACT_SILU 2
+#define KB_ACT_GELU_TANH 3
+__device__ __forceinline__ float kb_act(float z, int act) {
+    switch (act) {
+        case KB_ACT_RELU2: {
+            const float r = fmaxf(z, 0.0f);
+            return r * r;
+        }
+        case KB_ACT_SILU: return z / (1.0f + expf(-z));
+        case KB_ACT_GELU_TANH:
+            return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        default: return z;
+    }
+}
+
 #define KB_LAUNCH_RET() return (int)cudaGetLastError()
 
 // Programmatic dependent launch. Every kernel of the library begins with kb_pdl_launch() (when its grid is small,

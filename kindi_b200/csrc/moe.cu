@@ -19,24 +19,6 @@
 #include "common.cuh"
 #include <math.h>
 
-#define KB_ACT_NONE 0
-#define KB_ACT_RELU2 1
-#define KB_ACT_SILU 2
-#define KB_ACT_GELU_TANH 3
-
-__device__ __forceinline__ float kb_act(float z, int act) {
-    switch (act) {
-        case KB_ACT_RELU2: {
-            const float r = fmaxf(z, 0.0f);
-            return r * r;
-        }
-        case KB_ACT_SILU: return z / (1.0f + expf(-z));
-        case KB_ACT_GELU_TANH:
-            return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-        default: return z;
-    }
-}
-
 #define MOE_MAX_TOP 32
 
 __global__ void __launch_bounds__(128) k_moe_topk(const float* KB_STEP_DATA logits, int ldz,

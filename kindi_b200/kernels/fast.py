@@ -281,6 +281,25 @@ def attention_decode_rope(ctx, qkv, out, nh, nkv, hd, scale, window, inv_freq, r
     return True
 
 
+def _moe_bn(n: int, n_pairs: int) -> int:
+    """columns of a unit: narrow units while the rows are few (the step streams the experts' weights, and more units
+    spread that over more SMs), wide ones for prompt-sized steps"""
+    return 64 if n <= 64 else 128 if (n <= 128 or n_pairs <= 2048) else 256
+
+
 def moe_experts(ctx, y, idx, wts, wup, wdown, top, act):
-    """the experts' grouped products on the tensor cores, where a kernel takes the shape; None: not taken"""
-    return None
+    """the experts' grouped products on the tensor cores, where the kernel takes the shape (bf16, width and expert
+    size multiples of 8): 32-bit planes [top, T, width]; None: not taken"""
+    T, width = y.shape
+    E, F, _ = wup.shape
+    if not (y.dtype == wup.dtype == wdown.dtype == torch.bfloat16 and width % 8 == 0 and F % 8 == 0
+            and y.stride(1) == 1 and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0):
+        return None
+    plan = K.moe_plan(idx, E, K.moe_gemm_tc_tile())
+    ys = torch.empty((T * top, width), dtype=torch.bfloat16, device=y.device)
+    K.moe_gather(y, ys, plan, top)
+    h = torch.empty((T * top, F), dtype=torch.bfloat16, device=y.device)
+    K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status)
+    planes = torch.empty((top, T, width), dtype=torch.float32, device=y.device)
+    K.moe_gemm_tc(h, wdown, planes, plan, wts, top, "none", up=False, bn=_moe_bn(width, T * top), status=ctx.status)
+    return planes

@@ -50,6 +50,11 @@ _SIGS = {
     "kb_moe_topk": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "kb_moe_plan": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "kb_moe_gemm_tile": [],
+    "kb_moe_gemm_tc_tile": [],
+    "kb_moe_gemm_tc": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int,
+                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                       c_void_p, c_void_p],
+    "kb_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "kb_moe_gemm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int,
                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -117,7 +122,7 @@ class KernelTiming:
     def __getattr__(self, name):                       # stands in for the library while timing is on
         fn = getattr(_lib, name)
         if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits", "kb_rope_table_min_rows",
-                                                  "kb_moe_gemm_tile"):
+                                                  "kb_moe_gemm_tile", "kb_moe_gemm_tc_tile"):
             return fn
 
         def timed(*args):
@@ -414,6 +419,42 @@ def moe_gemm_down(h: torch.Tensor, w: torch.Tensor, plan: MoePlan, wts: torch.Te
                               planes.stride(0), N, F, plan.max_tiles, _p(plan.n_tiles), _p(plan.tile_e),
                               _p(plan.tile_r0), _p(plan.offs), _p(plan.perm), _p(wts), top, 0, 0, _stream()),
            "moe_gemm_down")
+
+
+@functools.lru_cache(maxsize=1)
+def moe_gemm_tc_tile() -> int:
+    return load().kb_moe_gemm_tc_tile()
+
+
+def moe_gather(y: torch.Tensor, out: torch.Tensor, plan: MoePlan, top: int) -> None:
+    """out[r] = y[token of pair perm[r]]: the activation rows in the plan's order (bf16, width a multiple of 8)"""
+    _need_cuda(y, out)
+    assert y.dtype == out.dtype == torch.bfloat16 and y.stride(1) == 1 and out.is_contiguous()
+    assert out.shape == (plan.n_pairs, y.shape[1])
+    _check(load().kb_moe_gather(_p(y), y.stride(0), _p(out), y.shape[1], _p(plan.perm), plan.n_pairs, top, _stream()),
+           "moe_gather")
+
+
+def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: MoePlan, wts: Optional[torch.Tensor],
+                top: int, act: str, *, up: bool, bn: int, status: torch.Tensor) -> None:
+    """the experts' grouped product on the tensor cores over the plan's tiles of 128 sorted rows. a: sorted rows
+    [n_pairs, K] bf16; w [E, N, K] bf16. up: out = act(a w[e]^T) as bf16 [n_pairs, N]; else out = float planes
+    [top, T, N] with plane k of a row's token = its k-th weight * (a w[e]^T)"""
+    _need_cuda(a, w, out, wts)
+    E, N, Kd = w.shape
+    assert a.dtype == w.dtype == torch.bfloat16 and a.shape == (plan.n_pairs, Kd) and a.stride(1) == 1
+    assert w.is_contiguous() and plan.tile == moe_gemm_tc_tile() and bn in (64, 128, 256)
+    if up:
+        assert out.dtype == torch.bfloat16 and out.shape == (plan.n_pairs, N) and out.stride(1) == 1
+        ldc, pstride = out.stride(0), 0
+    else:
+        assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[0] == top and out.shape[2] == N
+        assert wts is not None and wts.dtype == torch.float32 and wts.is_contiguous() and wts.numel() == plan.n_pairs
+        ldc, pstride = N, out.stride(0)
+    _check(load().kb_moe_gemm_tc(_p(a), plan.n_pairs, a.stride(0), _p(w), E, N, Kd, _p(out), ldc, pstride,
+                                 plan.max_tiles, _p(plan.n_tiles), _p(plan.tile_e), _p(plan.tile_r0), _p(plan.offs),
+                                 _p(plan.perm), _p(wts), top, ACT[act], 1 if up else 0, bn, _p(status), _stream()),
+           "moe_gemm_tc")
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
