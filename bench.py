@@ -121,6 +121,109 @@ def build_engine(layers: int, ctx: int, max_batch: int, base=None):
     return eng
 
 
+def engine_from_config(cfg: dict, ctx: int, max_batch: int):
+    """an engine over seeded random weights for any registered architecture's config.json object"""
+    import torch
+    from kindi_b200.config import model_from_config
+    from kindi_b200.engine.engine import Engine
+    from kindi_b200.parts.model import expected_tensors, tensor_inits
+    from kindi_b200.weights.random_init import random_tensors
+    mc, spec = model_from_config(cfg)
+    tensors = random_tensors(expected_tensors(spec), seed=0, std=0.02, dtype=torch.bfloat16, device="cuda:0",
+                             inits=tensor_inits(spec))
+    eng = Engine(spec=spec, tensors=tensors, ctx=ctx, dtype="bfloat16", max_batch=max_batch)
+    eng.config = mc
+    return eng
+
+
+# ---------------------------------------------------------------------------------------------- --arch vozinex
+# Layer sizes that resemble real models' (random weights, four layers), each beside the dense Llama-arch decoder of
+# the same width, heads, head size, window and vocabulary whose SwiGLU feed-forward has as many ACTIVE weights as a
+# row's chosen experts: 3 E F = top * 2 E ff.
+VOZINEX_SIZES = {
+    "s": dict(width=1024, heads=8, kv=2, experts=16, top=4, ff=512),
+    "m": dict(width=2048, heads=16, kv=4, experts=32, top=4, ff=1024),
+    "l": dict(width=4096, heads=32, kv=8, experts=32, top=4, ff=2048),
+}
+VOZINEX_LAYERS, VOZINEX_VOCAB, VOZINEX_WINDOW, VOZINEX_HEAD = 4, 32768, 1024, 128
+
+
+def vozinex_pair(sz: dict):
+    """(Vozinex config, dense Llama-arch config of equal size)"""
+    mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": VOZINEX_HEAD, "vdim": VOZINEX_HEAD,
+             "scale": VOZINEX_HEAD ** -0.5, "rot": {"base": 10000.0, "dims": VOZINEX_HEAD // 2},
+             "mask": {"size": VOZINEX_WINDOW, "keep_first": 4}}
+    mlp = {"kind": "moe", "expert": {"ff": sz["ff"]}, "router": {"experts": sz["experts"], "top": sz["top"]}}
+    voz = {"architecture": "Vozinex", "vocab": VOZINEX_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},
+           "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(VOZINEX_LAYERS)],
+           "loop": {"start": 0, "stop": 0, "times": 1}}
+    f_dense = (sz["top"] * 2 * sz["ff"] // 3 + 31) // 32 * 32
+    dense = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=VOZINEX_VOCAB,
+                 hidden_size=sz["width"], intermediate_size=f_dense, num_hidden_layers=VOZINEX_LAYERS,
+                 num_attention_heads=sz["heads"], num_key_value_heads=sz["kv"], head_dim=VOZINEX_HEAD,
+                 rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False, sliding_window=VOZINEX_WINDOW)
+    return voz, dense, f_dense
+
+
+def _grouped(summary: dict) -> dict:
+    """per kind of launch -> microseconds, the products' sizes dropped from the label"""
+    out = {}
+    for label, v in summary.items():
+        k = label.split(" ")[0]
+        out[k] = round(out.get(k, 0.0) + v["us"], 1)
+    return out
+
+
+def bench_vozinex(a) -> int:
+    """prefill and decode throughput of the Vozinex design at three layer sizes, each beside the dense decoder of equal
+    size, with the device time per kind of launch and the feed-forwards' fractions of the roofline"""
+    import torch
+    pk = peaks()
+    batch, context, tokens = a.batch, min(a.context, 4096), a.prefill_tokens
+    sizes = [x for x in (a.sizes or "s,m,l").split(",") if x in VOZINEX_SIZES]
+    rows = {}
+    for name in sizes:
+        sz = VOZINEX_SIZES[name]
+        voz, dense, f_dense = vozinex_pair(sz)
+        ctx = batch * (context + a.steps + a.warmup + 320) + tokens + 64
+        row = {"sizes": dict(sz, layers=VOZINEX_LAYERS, head=VOZINEX_HEAD, window=VOZINEX_WINDOW, dense_ff=f_dense)}
+        for what, cfg in (("vozinex", voz), ("dense", dense)):
+            eng = engine_from_config(cfg, ctx, batch)
+            for g in eng.cache.groups:
+                g.pool.normal_(0.0, 1.0)
+            dev_ms, _, launches, _ = bench_decode(eng, batch, context, a.steps, max(3, a.warmup), False)
+            pms = bench_prefill(eng, 3, 5, tokens)
+            kt = kernel_times(eng, batch, context, tokens)
+            row[what] = {"decode_ms": round(dev_ms, 4), "decode_tokens_per_s": round(batch * 1000.0 / dev_ms, 1),
+                         "launches_per_step": launches // a.steps, "prefill_ms": round(pms, 3),
+                         "prefill_tokens_per_s": round(tokens * 1000.0 / pms, 1),
+                         "kernels_us": {k: _grouped(v) for k, v in kt.items()}}
+            del eng
+            torch.cuda.empty_cache()
+        # the feed-forwards against their rooflines (per layer): a decode step streams the chosen experts' weights (the
+        # expected number of distinct experts among batch * top uniform picks), a prompt pass is bound by the products
+        E, ff, top, nx, L = sz["width"], sz["ff"], sz["top"], sz["experts"], VOZINEX_LAYERS
+        distinct = nx * (1.0 - (1.0 - 1.0 / nx) ** (batch * top))
+        dk, pkk = "decode_step_b%d_ctx%d" % (batch, context), "prompt_pass_%d" % tokens
+        v_us, d_us = row["vozinex"]["kernels_us"], row["dense"]["kernels_us"]
+        moe_dec = (v_us[dk].get("moe_gemm_tc", 0.0) + v_us[dk].get("moe_gather", 0.0)) / L
+        moe_pre = (v_us[pkk].get("moe_gemm_tc", 0.0) + v_us[pkk].get("moe_gather", 0.0)) / L
+        row["feed_forward_roofline"] = {
+            "vozinex_decode_us": round(moe_dec, 1),
+            "vozinex_decode_frac_of_copy_peak": round(distinct * 2 * E * ff * 2 / (moe_dec * 1e-6) / (pk["hbm_gbs"] * 1e9), 3)
+            if moe_dec else None,
+            "vozinex_prefill_us": round(moe_pre, 1),
+            "vozinex_prefill_frac_of_gemm_peak": round(tokens * top * 4.0 * E * ff / (moe_pre * 1e-6) / (pk["bf16_tflops"] * 1e12), 3)
+            if moe_pre else None,
+            "expected_distinct_experts": round(distinct, 1)}
+        rows[name] = row
+    print(json.dumps({"arch": "vozinex", "what": "prefill and decode of the Vozinex design beside the dense Llama-arch "
+                      "decoder of equal size (random weights, %d layers); not the default benchmark" % VOZINEX_LAYERS,
+                      "batch": batch, "context": context, "prefill_tokens": tokens, "steps": a.steps, "dtype": "bf16",
+                      "peaks": pk, "sizes": rows}))
+    return 0
+
+
 def prefill_flops(mc, T: int) -> float:
     E, F, nh, nkv, hd, L = (mc.hidden_size, mc.intermediate_size, mc.num_attention_heads, mc.num_key_value_heads,
                             mc.head_dim, mc.num_hidden_layers)
@@ -475,6 +578,10 @@ def main(argv=None) -> int:
                          "0.7, top-p 0.8, top-k 20) and report it as e2e_sampled")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill (for profiling)")
+    ap.add_argument("--arch", default="nanbeige", choices=("nanbeige", "vozinex"),
+                    help="vozinex: not the default benchmark but the Vozinex design at a few layer sizes, each beside "
+                         "the dense decoder of equal size (prefill, decode, device time per kind of launch)")
+    ap.add_argument("--sizes", default="", help="with --arch vozinex: which of s,m,l (default: all)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="prompt length of --prefill-only (the full run always measures 2048 tokens)")
     a = ap.parse_args(argv)
@@ -497,6 +604,8 @@ def main(argv=None) -> int:
                           "prefill": {"tokens": PREFILL_TOKENS, "ms": round(r["prefill_ms"], 3),
                                       "value": round(PREFILL_TOKENS * 1000.0 / r["prefill_ms"], 1)}}))
         return 0
+    if a.arch == "vozinex" and a.gpus == 1:
+        return bench_vozinex(a)
     if a.gpus != 1:
         print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
         return 2
