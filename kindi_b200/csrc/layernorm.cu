@@ -86,6 +86,66 @@ __global__ void __launch_bounds__(LN_THREADS) k_add_layernorm(float* KB_STEP_DAT
                                         kb_to_f<TW>(bias[i])));
 }
 
+// The same operation with one warp per row and the row in registers, for prompt-sized steps of the bfloat16 path: no
+// shared memory, no block barrier. Its sums are taken in another order than k_add_layernorm's, so the true 32-bit path,
+// whose results must not depend on how many rows a step has, never uses it. NC float4 per lane: widths up to 128 * NC.
+#define LN_WARP_MIN_T 64
+template <typename TW, int NC>
+__global__ void __launch_bounds__(256) k_add_layernorm_warp(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, const TW* __restrict__ bias, float eps,
+        bf16* __restrict__ y, int T, int E, int write_back) {
+    kb_pdl_launch();
+    kb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= T) return;
+    float* xr = x + (size_t)t * E;
+    const float* dr = delta + (size_t)t * E;
+    float4 v[NC];
+    float s = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const int i = (c * 32 + lane) * 4;
+        v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < E) {
+            v[c] = *(const float4*)(xr + i);
+            for (int p = 0; p < n_delta; p++) {
+                const float4 d = *(const float4*)(dr + (size_t)p * delta_stride + i);
+                v[c].x += d.x;
+                v[c].y += d.y;
+                v[c].z += d.z;
+                v[c].w += d.w;
+            }
+            if (write_back) *(float4*)(xr + i) = v[c];
+            s += (v[c].x + v[c].y) + (v[c].z + v[c].w);
+        }
+    }
+    const float mean = kb_warp_sum(s) / (float)E;
+    float q = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const int i = (c * 32 + lane) * 4;
+        if (i < E) {
+            const float a = v[c].x - mean, b = v[c].y - mean, cc = v[c].z - mean, d = v[c].w - mean;
+            q += (a * a + b * b) + (cc * cc + d * d);
+        }
+    }
+    const float inv = 1.0f / sqrtf(kb_warp_sum(q) / (float)E + eps);
+    bf16* yr = y + (size_t)t * E;
+#pragma unroll
+    for (int c = 0; c < NC; c++) {
+        const int i = (c * 32 + lane) * 4;
+        if (i < E) {
+            const float o0 = __fadd_rn(__fmul_rn(__fmul_rn(v[c].x - mean, inv), kb_to_f<TW>(w[i])), kb_to_f<TW>(bias[i]));
+            const float o1 = __fadd_rn(__fmul_rn(__fmul_rn(v[c].y - mean, inv), kb_to_f<TW>(w[i + 1])), kb_to_f<TW>(bias[i + 1]));
+            const float o2 = __fadd_rn(__fmul_rn(__fmul_rn(v[c].z - mean, inv), kb_to_f<TW>(w[i + 2])), kb_to_f<TW>(bias[i + 2]));
+            const float o3 = __fadd_rn(__fmul_rn(__fmul_rn(v[c].w - mean, inv), kb_to_f<TW>(w[i + 3])), kb_to_f<TW>(bias[i + 3]));
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+            *(uint2*)(yr + i) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+        }
+    }
+}
+
 extern "C" int kb_add_layernorm(float* x, const float* delta, int n_delta, long long delta_stride, const void* w,
                                 const void* bias, int wdtype, float eps, void* y, int ydtype, const int* rows,
                                 int n_out, int T, int E, int write_back, int* status, cudaStream_t st) {
@@ -95,6 +155,26 @@ extern "C" int kb_add_layernorm(float* x, const float* delta, int n_delta, long 
     const int vec = (E % 4 == 0) && (((uintptr_t)x) % 16 == 0) && (((uintptr_t)delta) % 16 == 0) &&
                     (delta_stride % 4 == 0);
     cudaError_t e = cudaSuccess;
+    if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= LN_WARP_MIN_T && E <= 128 * 32 &&
+        (write_back || n_delta == 0) && (((uintptr_t)y) % 8) == 0) {
+#define KB_LNW(NC)                                                                                                 \
+    do {                                                                                                           \
+        if (wdtype == KB_F32)                                                                                      \
+            e = kb_launch(k_add_layernorm_warp<float, NC>, (T + 7) / 8, 256, 0, st, x, delta, n_delta,             \
+                          (size_t)delta_stride, (const float*)w, (const float*)bias, eps, (bf16*)y, T, E,          \
+                          write_back);                                                                             \
+        else                                                                                                       \
+            e = kb_launch(k_add_layernorm_warp<bf16, NC>, (T + 7) / 8, 256, 0, st, x, delta, n_delta,              \
+                          (size_t)delta_stride, (const bf16*)w, (const bf16*)bias, eps, (bf16*)y, T, E,            \
+                          write_back);                                                                             \
+        return (int)e;                                                                                             \
+    } while (0)
+        if (E <= 128 * 4) KB_LNW(4);
+        if (E <= 128 * 8) KB_LNW(8);
+        if (E <= 128 * 16) KB_LNW(16);
+        KB_LNW(32);
+#undef KB_LNW
+    }
 #define KB_LN(TY, TW)                                                                                              \
     do {                                                                                                           \
         if (sm > 48 * 1024)                                                                                        \

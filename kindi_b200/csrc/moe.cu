@@ -59,11 +59,79 @@ __global__ void __launch_bounds__(128) k_moe_topk(const float* KB_STEP_DATA logi
     }
 }
 
+// The same pick with a warp per row, for up to 32 * MOE_PER experts: lane l holds the values of experts l, l + 32, ...
+// in registers; each of the `top` rounds takes the largest value not yet taken (of equal values the lower index), found
+// by a lane-local scan and five shuffle steps. The chosen values and their softmax are the same bits as k_moe_topk's.
+#define MOE_PER 8
+__global__ void __launch_bounds__(128) k_moe_topk_warp(const float* KB_STEP_DATA logits, int ldz,
+        const float* __restrict__ bias, int T, int E, int top, int* __restrict__ idx, float* __restrict__ wts) {
+    kb_pdl_launch();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    float b[MOE_PER];
+#pragma unroll
+    for (int j = 0; j < MOE_PER; j++) b[j] = (bias && lane + 32 * j < E) ? bias[lane + 32 * j] : 0.0f;
+    kb_pdl_wait();
+    if (t >= T) return;
+    const float* z = logits + (size_t)t * ldz;
+    float v[MOE_PER];
+    bool free_[MOE_PER];
+#pragma unroll
+    for (int j = 0; j < MOE_PER; j++) {
+        const int e = lane + 32 * j;
+        free_[j] = e < E;
+        v[j] = free_[j] ? z[e] + b[j] : 0.0f;
+    }
+    float my_val = 0.0f, mx = 0.0f, sum = 0.0f;          // lane k keeps the k-th chosen value
+    int my_idx = 0;
+    for (int k = 0; k < top; k++) {
+        // the lane's best free entry; "none" = index E (loses against every real entry)
+        int be = E;
+        float bv = 0.0f;
+#pragma unroll
+        for (int j = 0; j < MOE_PER; j++) {
+            const int e = lane + 32 * j;
+            if (free_[j] && (be == E || v[j] > bv)) {
+                be = e;
+                bv = v[j];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            // the other wins when it is a real entry and (this is none, or it is larger, or equal with a lower index)
+            if (oe < E && (be == E || ov > bv || (ov == bv && oe < be) || (bv != bv && oe < be))) {
+                bv = ov;
+                be = oe;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < MOE_PER; j++)
+            if (lane + 32 * j == be) free_[j] = false;
+        if (lane == k) {
+            my_val = bv;
+            my_idx = be;
+        }
+        mx = k == 0 ? bv : fmaxf(mx, bv);
+    }
+    // softmax over the chosen values, summed in the order they were chosen
+    const float ex = lane < top ? expf(my_val - mx) : 0.0f;
+    for (int k = 0; k < top; k++) sum += __shfl_sync(0xffffffffu, ex, k);
+    if (lane < top) {
+        idx[(size_t)t * top + lane] = my_idx < E ? my_idx : 0;
+        wts[(size_t)t * top + lane] = ex / sum;
+    }
+}
+
 extern "C" int kb_moe_topk(const float* logits, int ldz, const float* bias, int T, int E, int top, int* idx,
                            float* wts, cudaStream_t st) {
     if (T <= 0) return 0;
     if (top < 1 || top > MOE_MAX_TOP || top > E) return (int)cudaErrorInvalidValue;
-    kb_launch(k_moe_topk, (T + 127) / 128, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts);
+    if (E <= 32 * MOE_PER)
+        kb_launch(k_moe_topk_warp, (T + 3) / 4, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts);
+    else
+        kb_launch(k_moe_topk, (T + 127) / 128, 128, 0, st, logits, ldz, bias, T, E, top, idx, wts);
     KB_LAUNCH_RET();
 }
 

@@ -447,3 +447,50 @@ def test_trace_run_and_command_line_as_programs(tmp_path):
     r = subprocess.run([sys.executable, "-m", "kindi_b200", "--model", folder, "info"], capture_output=True, text=True,
                        cwd=ROOT, env=env, timeout=600)
     assert r.returncode == 0 and "Vozinex" in r.stdout + r.stderr, r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["C", "D"])
+def test_recorded_prompt_steps_and_their_padding_rows(tmp_path, name, dtype):
+    """short prompt steps are padded to a multiple of 64 rows and replayed from a recording once their shape has come
+    twice: the padding rows go through the norms, the router and the experts like any row, store nothing and change no
+    other row; in 32-bit a recorded step gives the bits of an engine that records nothing"""
+    from kindi_b200.engine.batch import StepEntry
+    from kindi_b200.engine.engine import Engine
+    raw = TV.TINY[name][0]
+    folder = TV.make_model(tmp_path, name, dtype)
+    m = PV.load_model(folder)
+    rng = random.Random(9)
+    eng = Engine(folder, ctx=4096, dtype=dtype, max_batch=4)
+    plain_eng = Engine(folder, ctx=4096, dtype=dtype, max_batch=4, cuda_graphs=False)
+
+    def run(e, groups, follow=3):
+        out = []
+        for group in groups:
+            slots = [e.alloc() for _ in group]
+            k = [len(t) - follow for t in group]
+            logits = e.step([StepEntry(s, tuple(t[:n]), (n - 1,)) for s, t, n in zip(slots, group, k)])
+            rows = [[logits[i].cpu().numpy()] for i in range(len(group))]
+            for j in range(follow):
+                lg = e.step([StepEntry(s, (t[n + j],), (0,)) for s, t, n in zip(slots, group, k)])
+                for i in range(len(group)):
+                    rows[i].append(lg[i].cpu().numpy())
+            e.check_status()
+            for s in slots:
+                e.free(s)
+            out.append([np.stack(r) for r in rows])
+        return out
+
+    lengths = [[103], [93], [131], [68], [73], [40, 71], [64, 9], [8, 100], [200], [260], [300]]
+    groups = [[TV.needle_request(raw["vocab"], n, 1, list(range(n - 5, n)), rng) for n in g] for g in lengths]
+    got = run(eng, groups)
+    assert sum(1 for k in eng._graphs if k[0] == "prompt") >= 2 and eng.graph_replays >= 6
+    same = run(plain_eng, groups)
+    for g, mine, other in zip(groups, got, same):
+        for toks, a, b in zip(g, mine, other):
+            want = PV.forward(m, toks).numpy()[len(toks) - 4:]
+            assert tiny.rel_err(a, want) <= TOL[dtype], (len(toks), tiny.rel_err(a, want))
+            if dtype == "float32":
+                assert np.array_equal(a, b), len(toks)
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
