@@ -88,7 +88,8 @@ __global__ void __launch_bounds__(LN_THREADS) k_add_layernorm(float* KB_STEP_DAT
 
 // The same operation with one warp per row and the row in registers, for prompt-sized steps of the bfloat16 path: no
 // shared memory, no block barrier. Its sums are taken in another order than k_add_layernorm's, so the true 32-bit path,
-// whose results must not depend on how many rows a step has, never uses it. NC float4 per lane: widths up to 128 * NC.
+// whose results must not depend on how many rows a step has, never uses it. NC float4 per lane: widths up to 128 * NC
+// (up to 2048: at 4096 the row no longer fits the registers of enough resident warps, and the block per row is faster).
 #define LN_WARP_MIN_T 64
 template <typename TW, int NC>
 __global__ void __launch_bounds__(256) k_add_layernorm_warp(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
@@ -155,7 +156,7 @@ extern "C" int kb_add_layernorm(float* x, const float* delta, int n_delta, long 
     const int vec = (E % 4 == 0) && (((uintptr_t)x) % 16 == 0) && (((uintptr_t)delta) % 16 == 0) &&
                     (delta_stride % 4 == 0);
     cudaError_t e = cudaSuccess;
-    if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= LN_WARP_MIN_T && E <= 128 * 32 &&
+    if (ydtype == KB_BF16 && vec && rows == nullptr && n_out == T && T >= LN_WARP_MIN_T && E <= 128 * 16 &&
         (write_back || n_delta == 0) && (((uintptr_t)y) % 8) == 0) {
 #define KB_LNW(NC)                                                                                                 \
     do {                                                                                                           \
@@ -171,8 +172,7 @@ extern "C" int kb_add_layernorm(float* x, const float* delta, int n_delta, long 
     } while (0)
         if (E <= 128 * 4) KB_LNW(4);
         if (E <= 128 * 8) KB_LNW(8);
-        if (E <= 128 * 16) KB_LNW(16);
-        KB_LNW(32);
+        KB_LNW(16);
 #undef KB_LNW
     }
 #define KB_LN(TY, TW)                                                                                              \
