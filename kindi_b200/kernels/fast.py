@@ -287,19 +287,46 @@ def _moe_bn(n: int, n_pairs: int) -> int:
     return 64 if n <= 64 else 128 if (n <= 128 or n_pairs <= 2048) else 256
 
 
+def _moe_tc_ok(y, wup, wdown) -> bool:
+    width, F = y.shape[1], wup.shape[1]
+    return (y.dtype == wup.dtype == wdown.dtype == torch.bfloat16 and width % 8 == 0 and F % 8 == 0
+            and y.stride(1) == 1 and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0)
+
+
+# the one-block router of a decode-sized step reads the router's weights through one SM: worth it up to this size
+MOE_SMALL_ROUTER_BYTES = 512 * 1024
+
+
+def moe_decode_step(ctx, y, wr, br, wup, wdown, top, act):
+    """the whole feed-forward of a decode-sized step (up to 32 rows): router, pick, plan and gather in one launch,
+    then the two grouped products on the tensor cores; None: not taken"""
+    T, width = y.shape
+    E, F, _ = wup.shape
+    if not (_moe_tc_ok(y, wup, wdown) and T <= K.moe_route_small_max_rows() and E <= 256 and top <= 32
+            and wr.is_contiguous() and wr.data_ptr() % 16 == 0
+            and wr.numel() * wr.element_size() <= MOE_SMALL_ROUTER_BYTES):
+        return None
+    idx, wts, plan, ys = K.moe_route_small(y, wr, br, top, K.moe_gemm_tc_tile())
+    return _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T)
+
+
+def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T):
+    E, F, width = wup.shape
+    h = torch.empty((T * top, F), dtype=torch.bfloat16, device=ys.device)
+    K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status)
+    planes = torch.empty((top, T, width), dtype=torch.float32, device=ys.device)
+    K.moe_gemm_tc(h, wdown, planes, plan, wts, top, "none", up=False, bn=_moe_bn(width, T * top), status=ctx.status)
+    return planes
+
+
 def moe_experts(ctx, y, idx, wts, wup, wdown, top, act):
     """the experts' grouped products on the tensor cores, where the kernel takes the shape (bf16, width and expert
     size multiples of 8): 32-bit planes [top, T, width]; None: not taken"""
     T, width = y.shape
     E, F, _ = wup.shape
-    if not (y.dtype == wup.dtype == wdown.dtype == torch.bfloat16 and width % 8 == 0 and F % 8 == 0
-            and y.stride(1) == 1 and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0):
+    if not _moe_tc_ok(y, wup, wdown):
         return None
     plan = K.moe_plan(idx, E, K.moe_gemm_tc_tile())
     ys = torch.empty((T * top, width), dtype=torch.bfloat16, device=y.device)
     K.moe_gather(y, ys, plan, top)
-    h = torch.empty((T * top, F), dtype=torch.bfloat16, device=y.device)
-    K.moe_gemm_tc(ys, wup, h, plan, None, top, act, up=True, bn=_moe_bn(F, T * top), status=ctx.status)
-    planes = torch.empty((top, T, width), dtype=torch.float32, device=y.device)
-    K.moe_gemm_tc(h, wdown, planes, plan, wts, top, "none", up=False, bn=_moe_bn(width, T * top), status=ctx.status)
-    return planes
+    return _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T)

@@ -54,6 +54,9 @@ _SIGS = {
     "kb_moe_gemm_tc": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int,
                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                        c_void_p, c_void_p],
+    "kb_moe_route_small_max_rows": [],
+    "kb_moe_route_small": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "kb_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "kb_moe_gemm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int,
                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -122,7 +125,8 @@ class KernelTiming:
     def __getattr__(self, name):                       # stands in for the library while timing is on
         fn = getattr(_lib, name)
         if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits", "kb_rope_table_min_rows",
-                                                  "kb_moe_gemm_tile", "kb_moe_gemm_tc_tile"):
+                                                  "kb_moe_gemm_tile", "kb_moe_gemm_tc_tile",
+                                                  "kb_moe_route_small_max_rows"):
             return fn
 
         def timed(*args):
@@ -366,16 +370,11 @@ class MoePlan:
     __slots__ = ("n_pairs", "n_experts", "tile", "max_tiles", "offs", "perm", "tile_e", "tile_r0", "n_tiles")
 
 
-def moe_plan(idx: torch.Tensor, n_experts: int, tile: int) -> MoePlan:
-    _need_cuda(idx)
-    assert idx.dtype == torch.int32 and idx.is_contiguous()
-    n = idx.numel()
-    if n_experts > 4096:
-        raise KernelError("kindi_b200: up to 4096 experts, found %d" % n_experts)
+def _new_plan(n: int, n_experts: int, tile: int, device) -> MoePlan:
     pl = MoePlan()
     pl.n_pairs, pl.n_experts, pl.tile = n, n_experts, tile
     pl.max_tiles = -(-n // tile) + min(n_experts, n)
-    buf = torch.empty(n_experts + 1 + n + 2 * pl.max_tiles + 1, dtype=torch.int32, device=idx.device)
+    buf = torch.empty(n_experts + 1 + n + 2 * pl.max_tiles + 1, dtype=torch.int32, device=device)
     a = 0
     pl.offs = buf[a:a + n_experts + 1]
     a += n_experts + 1
@@ -386,6 +385,16 @@ def moe_plan(idx: torch.Tensor, n_experts: int, tile: int) -> MoePlan:
     pl.tile_r0 = buf[a:a + pl.max_tiles]
     a += pl.max_tiles
     pl.n_tiles = buf[a:a + 1]
+    return pl
+
+
+def moe_plan(idx: torch.Tensor, n_experts: int, tile: int) -> MoePlan:
+    _need_cuda(idx)
+    assert idx.dtype == torch.int32 and idx.is_contiguous()
+    n = idx.numel()
+    if n_experts > 4096:
+        raise KernelError("kindi_b200: up to 4096 experts, found %d" % n_experts)
+    pl = _new_plan(n, n_experts, tile, idx.device)
     _check(load().kb_moe_plan(_p(idx), n, n_experts, tile, _p(pl.offs), _p(pl.perm), _p(pl.tile_e), _p(pl.tile_r0),
                               _p(pl.n_tiles), _stream()), "moe_plan")
     return pl
@@ -419,6 +428,32 @@ def moe_gemm_down(h: torch.Tensor, w: torch.Tensor, plan: MoePlan, wts: torch.Te
                               planes.stride(0), N, F, plan.max_tiles, _p(plan.n_tiles), _p(plan.tile_e),
                               _p(plan.tile_r0), _p(plan.offs), _p(plan.perm), _p(wts), top, 0, 0, _stream()),
            "moe_gemm_down")
+
+
+@functools.lru_cache(maxsize=1)
+def moe_route_small_max_rows() -> int:
+    return load().kb_moe_route_small_max_rows()
+
+
+def moe_route_small(y: torch.Tensor, wr: torch.Tensor, bias: Optional[torch.Tensor], top: int, tile: int):
+    """router, pick, plan and gather of a decode-sized step in one launch: y bf16 [T <= 32, K], wr [E <= 256, K] (bf16
+    or float32), K a multiple of 8. Returns (idx int32 [T, top], weights float32 [T, top], plan, the activation rows
+    in the plan's order bf16 [T top, K])"""
+    _need_cuda(y, wr, bias)
+    T, Kd = y.shape
+    E = wr.shape[0]
+    assert y.dtype == torch.bfloat16 and y.stride(1) == 1 and wr.is_contiguous() and wr.shape[1] == Kd
+    assert T <= moe_route_small_max_rows() and E <= 256 and 1 <= top <= min(E, 32)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous()
+    idx = torch.empty((T, top), dtype=torch.int32, device=y.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=y.device)
+    ys = torch.empty((T * top, Kd), dtype=torch.bfloat16, device=y.device)
+    pl = _new_plan(T * top, E, tile, y.device)
+    _check(load().kb_moe_route_small(_p(y), y.stride(0), _p(wr), dt(wr), _p(bias), T, E, Kd, top, tile, _p(idx),
+                                     _p(wts), _p(pl.offs), _p(pl.perm), _p(pl.tile_e), _p(pl.tile_r0), _p(pl.n_tiles),
+                                     _p(ys), _stream()), "moe_route_small")
+    return idx, wts, pl, ys
 
 
 @functools.lru_cache(maxsize=1)

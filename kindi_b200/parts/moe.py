@@ -19,7 +19,6 @@ import torch
 from ..config.registry import register_part
 from ..config.spec import PartSpec
 from ..kernels import lib as K
-from ..kernels import linear as L
 from ..kernels import moe as M
 from .base import Branch, FeedForward, StepContext, WeightView
 
@@ -73,9 +72,7 @@ class MixtureOfExperts(FeedForward):
         self.wdown = torch.stack(downs).contiguous()        # [E, width, f]
 
     def forward(self, ctx: StepContext, y: torch.Tensor) -> Branch:
-        logits = L.linear(ctx, y, self.wr, torch.float32)
-        idx, wts = K.moe_topk(logits, self.br, self.top)
-        return Branch(M.experts(ctx, y, idx, wts, self.wup, self.wdown, self.top, self.act, self.dtype))
+        return Branch(M.feed_forward(ctx, y, self.wr, self.br, self.wup, self.wdown, self.top, self.act, self.dtype))
 
     def bytes_read(self) -> int:
         """the router and, of the experts, the share a single row reads (a large step reads up to all of them)"""

@@ -58,7 +58,12 @@ VZ_D = _config(257, 200, 2e-6, [
 VZ_E = _config(131, 72, 1e-5, [
     _layer(5, 1, 24, 24, 0.2, 12, 30000.0, 17, 2, 7, 3, 20),
     _layer(5, 5, 24, 10, 0.2, 24, 30000.0, 17, 2, 7, 3, 20)], (0, 1, 2))
-TINY = {"A": (VZ_A, 11), "B": (VZ_B, 12), "C": (VZ_C, 13), "D": (VZ_D, 14), "E": (VZ_E, 15)}
+# F: sizes that no vector load or tensor-core tile takes: width 100, heads of 10 with values of 6, experts of 18, a
+#    window of 9 that keeps 2, a layer without a window, both layers run twice
+VZ_F = _config(97, 100, 1e-5, [
+    _layer(2, 1, 10, 6, 0.31, 4, 10000.0, 9, 2, 3, 2, 18),
+    _layer(2, 2, 10, 10, 0.31, 10, 10000.0, None, 0, 3, 2, 18)], (0, 2, 2))
+TINY = {"A": (VZ_A, 11), "B": (VZ_B, 12), "C": (VZ_C, 13), "D": (VZ_D, 14), "E": (VZ_E, 15), "F": (VZ_F, 16)}
 
 
 def make_model(tmp_path, name: str, dtype: str = "bfloat16", strength: float = 12.0) -> str:
