@@ -280,170 +280,3 @@ extern "C" int kb_moe_gather(const void* Y, int ldy, void* Ys, int K, const int*
     kb_launch(k_moe_gather, blocks, 256, 0, st, (const bf16*)Y, ldy, (bf16*)Ys, K, perm, n_pairs, top);
     KB_LAUNCH_RET();
 }
-
-// ------------------------------------------------------------------------------------------------------------------
-// Router, pick, plan and gather of a decode-sized step in ONE block: for up to 32 rows the four launches (router
-// product, k_moe_topk, k_moe_plan, k_moe_gather) cost more than their work. Warps take (row, expert) pairs and compute
-// the logit as a 32-bit sum over the width (bf16 rows and bf16 or 32-bit router weights, eight elements a load); warp t
-// then picks row t's experts exactly as k_moe_topk_warp does; the block counts, lays out the experts' stretches and
-// tiles, places the pairs and copies the activation rows into that order.
-#define RS_THREADS 1024
-#define RS_MAX_T 32
-#define RS_PER 8                     // experts a lane holds: up to 256 experts
-
-__device__ __forceinline__ void rs_load8(const bf16* p, float* o) {
-    const uint4 r = *(const uint4*)p;
-    const uint32_t u[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        o[2 * j] = __uint_as_float(u[j] << 16);
-        o[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-    }
-}
-__device__ __forceinline__ void rs_load8(const float* p, float* o) {
-    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
-    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-}
-
-template <typename TW>
-__global__ void __launch_bounds__(RS_THREADS) k_moe_route_small(const bf16* KB_STEP_DATA Y, int ldy,
-        const TW* __restrict__ Wr, const float* __restrict__ bias, int T, int E, int K, int top, int tile,
-        int* __restrict__ idx, float* __restrict__ wts, int* __restrict__ offs, int* __restrict__ perm,
-        int* __restrict__ tile_e, int* __restrict__ tile_r0, int* __restrict__ n_tiles, bf16* __restrict__ Ys) {
-    extern __shared__ __align__(16) uint8_t rs_raw[];
-    float* z = (float*)rs_raw;                       // [T][E] logits
-    int* counts = (int*)(z + T * E);                 // [E]
-    int* cursor = counts + E;                        // [E]
-    int* sidx = cursor + E;                          // [T * top]
-    int* sperm = sidx + T * top;                     // [T * top]
-    kb_pdl_launch();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int e = threadIdx.x; e < E; e += RS_THREADS) counts[e] = 0;
-    kb_pdl_wait();
-    // ---- logits
-    for (int p = warp; p < T * E; p += RS_THREADS / 32) {
-        const int t = p / E, e = p % E;
-        const bf16* yr = Y + (size_t)t * ldy;
-        const TW* wr = Wr + (size_t)e * K;
-        float acc = 0.0f;
-        for (int i = lane * 8; i < K; i += 256) {
-            float a[8], b[8];
-            rs_load8(yr + i, a);
-            rs_load8(wr + i, b);
-#pragma unroll
-            for (int j = 0; j < 8; j++) acc = fmaf(a[j], b[j], acc);
-        }
-        acc = kb_warp_sum(acc);
-        if (lane == 0) z[p] = acc + (bias ? bias[e] : 0.0f);
-    }
-    __syncthreads();
-    // ---- the pick of row t by warp t
-    if (warp < T) {
-        const int t = warp;
-        float v[RS_PER];
-        bool free_[RS_PER];
-#pragma unroll
-        for (int j = 0; j < RS_PER; j++) {
-            const int e = lane + 32 * j;
-            free_[j] = e < E;
-            v[j] = free_[j] ? z[t * E + e] : 0.0f;
-        }
-        float my_val = 0.0f, mx = 0.0f, sum = 0.0f;
-        int my_idx = 0;
-        for (int k = 0; k < top; k++) {
-            int be = E;
-            float bv = 0.0f;
-#pragma unroll
-            for (int j = 0; j < RS_PER; j++) {
-                const int e = lane + 32 * j;
-                if (free_[j] && (be == E || v[j] > bv)) {
-                    be = e;
-                    bv = v[j];
-                }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-                const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-                if (oe < E && (be == E || ov > bv || (ov == bv && oe < be) || (bv != bv && oe < be))) {
-                    bv = ov;
-                    be = oe;
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < RS_PER; j++)
-                if (lane + 32 * j == be) free_[j] = false;
-            if (lane == k) {
-                my_val = bv;
-                my_idx = be;
-            }
-            mx = k == 0 ? bv : fmaxf(mx, bv);
-        }
-        const float ex = lane < top ? expf(my_val - mx) : 0.0f;
-        for (int k = 0; k < top; k++) sum += __shfl_sync(0xffffffffu, ex, k);
-        if (lane < top) {
-            const int e = my_idx < E ? my_idx : 0;
-            idx[t * top + lane] = e;
-            wts[t * top + lane] = ex / sum;
-            sidx[t * top + lane] = e;
-            atomicAdd(&counts[e], 1);
-        }
-    }
-    __syncthreads();
-    // ---- the plan
-    const int n_pairs = T * top;
-    if (threadIdx.x == 0) {
-        int at = 0, nt = 0;
-        for (int e = 0; e < E; e++) {
-            offs[e] = at;
-            cursor[e] = at;
-            for (int r = 0; r < counts[e]; r += tile) {
-                tile_e[nt] = e;
-                tile_r0[nt] = at + r;
-                nt++;
-            }
-            at += counts[e];
-        }
-        offs[E] = at;
-        n_tiles[0] = nt;
-    }
-    __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += RS_THREADS) {
-        const int r = atomicAdd(&cursor[sidx[p]], 1);
-        perm[r] = p;
-        sperm[r] = p;
-    }
-    __syncthreads();
-    // ---- the activation rows in the plan's order
-    const int per_row = K / 8;
-    for (int i = threadIdx.x; i < n_pairs * per_row; i += RS_THREADS) {
-        const int r = i / per_row, c = i % per_row;
-        *(uint4*)(Ys + (size_t)r * K + c * 8) = *(const uint4*)(Y + (size_t)(sperm[r] / top) * ldy + c * 8);
-    }
-}
-
-extern "C" int kb_moe_route_small_max_rows() { return RS_MAX_T; }
-
-extern "C" int kb_moe_route_small(const void* Y, int ldy, const void* Wr, int wdtype, const float* bias, int T, int E,
-                                  int K, int top, int tile, int* idx, float* wts, int* offs, int* perm, int* tile_e,
-                                  int* tile_r0, int* n_tiles, void* Ys, cudaStream_t st) {
-    if (T <= 0) return 0;
-    if (T > RS_MAX_T || E > 32 * RS_PER || top < 1 || top > 32 || top > E || (K % 8) || (ldy % 8) || tile < 1 ||
-        ((uintptr_t)Y & 15) || ((uintptr_t)Wr & 15) || ((uintptr_t)Ys & 15))
-        return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)T * E * 4 + (size_t)2 * E * 4 + (size_t)2 * T * top * 4;
-    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    cudaError_t e;
-    if (wdtype == KB_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(k_moe_route_small<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = kb_launch(k_moe_route_small<float>, 1, RS_THREADS, smem, st, (const bf16*)Y, ldy, (const float*)Wr, bias, T,
-                      E, K, top, tile, idx, wts, offs, perm, tile_e, tile_r0, n_tiles, (bf16*)Ys);
-    } else {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(k_moe_route_small<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        e = kb_launch(k_moe_route_small<bf16>, 1, RS_THREADS, smem, st, (const bf16*)Y, ldy, (const bf16*)Wr, bias, T,
-                      E, K, top, tile, idx, wts, offs, perm, tile_e, tile_r0, n_tiles, (bf16*)Ys);
-    }
-    return (int)e;
-}

@@ -293,23 +293,6 @@ def _moe_tc_ok(y, wup, wdown) -> bool:
             and y.stride(1) == 1 and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0)
 
 
-# the one-block router of a decode-sized step reads the router's weights through one SM: worth it up to this size
-MOE_SMALL_ROUTER_BYTES = 512 * 1024
-
-
-def moe_decode_step(ctx, y, wr, br, wup, wdown, top, act):
-    """the whole feed-forward of a decode-sized step (up to 32 rows): router, pick, plan and gather in one launch,
-    then the two grouped products on the tensor cores; None: not taken"""
-    T, width = y.shape
-    E, F, _ = wup.shape
-    if not (_moe_tc_ok(y, wup, wdown) and T <= K.moe_route_small_max_rows() and E <= 256 and top <= 32
-            and wr.is_contiguous() and wr.data_ptr() % 16 == 0
-            and wr.numel() * wr.element_size() <= MOE_SMALL_ROUTER_BYTES):
-        return None
-    idx, wts, plan, ys = K.moe_route_small(y, wr, br, top, K.moe_gemm_tc_tile())
-    return _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T)
-
-
 def _moe_products(ctx, ys, plan, wts, wup, wdown, top, act, T):
     E, F, width = wup.shape
     h = torch.empty((T * top, F), dtype=torch.bfloat16, device=ys.device)

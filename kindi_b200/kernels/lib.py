@@ -54,9 +54,6 @@ _SIGS = {
     "kb_moe_gemm_tc": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int,
                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                        c_void_p, c_void_p],
-    "kb_moe_route_small_max_rows": [],
-    "kb_moe_route_small": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "kb_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "kb_moe_gemm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int,
                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -125,8 +122,7 @@ class KernelTiming:
     def __getattr__(self, name):                       # stands in for the library while timing is on
         fn = getattr(_lib, name)
         if not name.startswith("kb_") or name in ("kb_set_pdl", "kb_gemm_tc_splits", "kb_rope_table_min_rows",
-                                                  "kb_moe_gemm_tile", "kb_moe_gemm_tc_tile",
-                                                  "kb_moe_route_small_max_rows"):
+                                                  "kb_moe_gemm_tile", "kb_moe_gemm_tc_tile"):
             return fn
 
         def timed(*args):
@@ -428,32 +424,6 @@ def moe_gemm_down(h: torch.Tensor, w: torch.Tensor, plan: MoePlan, wts: torch.Te
                               planes.stride(0), N, F, plan.max_tiles, _p(plan.n_tiles), _p(plan.tile_e),
                               _p(plan.tile_r0), _p(plan.offs), _p(plan.perm), _p(wts), top, 0, 0, _stream()),
            "moe_gemm_down")
-
-
-@functools.lru_cache(maxsize=1)
-def moe_route_small_max_rows() -> int:
-    return load().kb_moe_route_small_max_rows()
-
-
-def moe_route_small(y: torch.Tensor, wr: torch.Tensor, bias: Optional[torch.Tensor], top: int, tile: int):
-    """router, pick, plan and gather of a decode-sized step in one launch: y bf16 [T <= 32, K], wr [E <= 256, K] (bf16
-    or float32), K a multiple of 8. Returns (idx int32 [T, top], weights float32 [T, top], plan, the activation rows
-    in the plan's order bf16 [T top, K])"""
-    _need_cuda(y, wr, bias)
-    T, Kd = y.shape
-    E = wr.shape[0]
-    assert y.dtype == torch.bfloat16 and y.stride(1) == 1 and wr.is_contiguous() and wr.shape[1] == Kd
-    assert T <= moe_route_small_max_rows() and E <= 256 and 1 <= top <= min(E, 32)
-    if bias is not None:
-        assert bias.dtype == torch.float32 and bias.numel() == E and bias.is_contiguous()
-    idx = torch.empty((T, top), dtype=torch.int32, device=y.device)
-    wts = torch.empty((T, top), dtype=torch.float32, device=y.device)
-    ys = torch.empty((T * top, Kd), dtype=torch.bfloat16, device=y.device)
-    pl = _new_plan(T * top, E, tile, y.device)
-    _check(load().kb_moe_route_small(_p(y), y.stride(0), _p(wr), dt(wr), _p(bias), T, E, Kd, top, tile, _p(idx),
-                                     _p(wts), _p(pl.offs), _p(pl.perm), _p(pl.tile_e), _p(pl.tile_r0), _p(pl.n_tiles),
-                                     _p(ys), _stream()), "moe_route_small")
-    return idx, wts, pl, ys
 
 
 @functools.lru_cache(maxsize=1)

@@ -15,11 +15,6 @@ def feed_forward(ctx, y: torch.Tensor, wr: torch.Tensor, br: Optional[torch.Tens
     """32-bit planes ``[top, T, width]`` whose sum in order is the feed-forward's output: router logits ``y wr^T + br``
     with 32-bit accumulation, the ``top`` largest per row weighted by the softmax over those alone, plane k of a row =
     its k-th weight times ``W_down[e] act(W_up[e] y)``"""
-    if ctx.fast:
-        from . import fast
-        planes = fast.moe_decode_step(ctx, y, wr, br, wup, wdown, top, act)
-        if planes is not None:
-            return planes
     logits = L.linear(ctx, y, wr, torch.float32)
     idx, wts = K.moe_topk(logits, br, top)
     return experts(ctx, y, idx, wts, wup, wdown, top, act, dtype)

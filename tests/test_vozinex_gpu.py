@@ -494,27 +494,3 @@ def test_recorded_prompt_steps_and_their_padding_rows(tmp_path, name, dtype):
                 assert np.array_equal(a, b), len(toks)
     eng.cache.check()
     assert eng.cache.slots.n_held == 0
-
-
-@pytest.mark.parametrize("T,E,top,width,F,wdtype", [(1, 5, 2, 64, 24, "bfloat16"), (8, 32, 4, 256, 64, "bfloat16"),
-                                                   (32, 12, 12, 128, 40, "bfloat16"), (7, 200, 8, 72, 16, "float32")])
-def test_decode_sized_router_pick_plan_and_gather_in_one_launch(K, T, E, top, width, F, wdtype):
-    """the one-block kernel of a decode-sized step against the plain router and pick, and its plan and gathered rows
-    against what they must hold"""
-    g = torch.Generator().manual_seed(T + E)
-    y = torch.randn(T, width, generator=g).to(torch.bfloat16)
-    wr = torch.randn(E, width, generator=g).to(DT[wdtype])
-    b = torch.randn(E, generator=g)
-    z = y.double() @ wr.double().T + b.double()
-    widx, ww = PV.route(z, top)
-    idx, w, plan, ys = K.moe_route_small(y.cuda(), wr.cuda(), b.cuda(), top, 128)
-    assert torch.equal(idx.cpu().long(), widx) and _rel(w, ww) < 1e-4
-    offs, perm = plan.offs.cpu().tolist(), plan.perm.cpu().tolist()
-    assert sorted(perm) == list(range(T * top)) and offs[0] == 0 and offs[-1] == T * top
-    flat = widx.reshape(-1).tolist()
-    for e in range(E):
-        assert sorted(flat[p] for p in perm[offs[e]:offs[e + 1]]) == [e] * (offs[e + 1] - offs[e])
-    nt = int(plan.n_tiles.item())
-    tiles = list(zip(plan.tile_e.cpu().tolist()[:nt], plan.tile_r0.cpu().tolist()[:nt]))
-    assert tiles == [(e, offs[e]) for e in range(E) if offs[e + 1] > offs[e]]      # (no expert has more than a tile here)
-    assert torch.equal(ys.cpu(), y[torch.tensor(perm) // top])
