@@ -8,7 +8,6 @@ r the rotated dimensions of a head, W the window, F the first positions a window
 from __future__ import annotations
 
 import json
-import math
 import os
 from typing import List, Optional, Sequence
 

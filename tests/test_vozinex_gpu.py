@@ -213,7 +213,7 @@ def test_attention_with_kept_first_positions(K, kind, dtype, hd, window, keep):
             assert err < tol, (kind, L, p, err)
 
 
-@pytest.mark.parametrize("T,E,top", [(1, 5, 2), (77, 12, 4), (300, 7, 7), (40, 64, 1), (9, 130, 8)])
+@pytest.mark.parametrize("T,E,top", [(1, 5, 2), (77, 11, 3), (300, 7, 7), (40, 64, 1), (9, 130, 8)])
 def test_router_pick_and_weights(K, T, E, top):
     g = torch.Generator().manual_seed(T + E)
     z, b = torch.randn(T, E, generator=g), torch.randn(E, generator=g)
