@@ -63,7 +63,16 @@ VZ_E = _config(131, 72, 1e-5, [
 VZ_F = _config(97, 100, 1e-5, [
     _layer(2, 1, 10, 6, 0.31, 4, 10000.0, 9, 2, 3, 2, 18),
     _layer(2, 2, 10, 10, 0.31, 10, 10000.0, None, 0, 3, 2, 18)], (0, 2, 2))
-TINY = {"A": (VZ_A, 11), "B": (VZ_B, 12), "C": (VZ_C, 13), "D": (VZ_D, 14), "E": (VZ_E, 15), "F": (VZ_F, 16)}
+# G: keys of 32 and values of 48, both widened to the 64 the tensor-core attention kernels take (five query heads per
+#    key/value head); then a layer with a key/value head per query head at head size 64; ten experts of 96, three per
+#    row; the middle layers run twice
+VZ_G = _config(401, 320, 1e-5, [
+    _layer(10, 2, 32, 48, 0.22, 16, 10000.0, 100, 6, 10, 3, 96),
+    _layer(10, 2, 32, 48, 0.22, 16, 10000.0, 100, 6, 10, 3, 96),
+    _layer(4, 4, 64, 64, 0.125, 64, 10000.0, 128, 64, 10, 3, 96),
+    _layer(4, 4, 64, 64, 0.125, 64, 10000.0, 65, 1)], (1, 3, 2))
+TINY = {"A": (VZ_A, 11), "B": (VZ_B, 12), "C": (VZ_C, 13), "D": (VZ_D, 14), "E": (VZ_E, 15), "F": (VZ_F, 16),
+        "G": (VZ_G, 17)}
 
 
 def make_model(tmp_path, name: str, dtype: str = "bfloat16", strength: float = 12.0) -> str:
