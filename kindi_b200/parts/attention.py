@@ -100,8 +100,8 @@ class CausalSelfAttention(Mixer):
         self.hd = self._cache_dim(spec)
         if self.nh % self.nkv:
             raise ValueError("n_heads %d is not a multiple of n_kv_heads %d" % (self.nh, self.nkv))
-        if self.hd % 2 or self.hd > 256:
-            raise ValueError("head_dim must be even and at most 256, found %d" % self.hd)
+        if self.hd > 256:
+            raise ValueError("head sizes up to 256 are supported, found %d" % self.hd)
         self.window = int(spec.get("window") or 0)
         self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
         if self.keep_first < 0:

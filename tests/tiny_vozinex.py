@@ -58,11 +58,11 @@ VZ_D = _config(257, 200, 2e-6, [
 VZ_E = _config(131, 72, 1e-5, [
     _layer(5, 1, 24, 24, 0.2, 12, 30000.0, 17, 2, 7, 3, 20),
     _layer(5, 5, 24, 10, 0.2, 24, 30000.0, 17, 2, 7, 3, 20)], (0, 1, 2))
-# F: sizes that no vector load or tensor-core tile takes: width 100, heads of 10 with values of 6, experts of 18, a
-#    window of 9 that keeps 2, a layer without a window, both layers run twice
+# F: sizes that no vector load or tensor-core tile takes: width 100, heads of 10 with values of 6, then heads of an odd
+#    size (9), experts of 18, a window of 9 that keeps 2, a layer without a window, both layers run twice
 VZ_F = _config(97, 100, 1e-5, [
     _layer(2, 1, 10, 6, 0.31, 4, 10000.0, 9, 2, 3, 2, 18),
-    _layer(2, 2, 10, 10, 0.31, 10, 10000.0, None, 0, 3, 2, 18)], (0, 2, 2))
+    _layer(2, 2, 9, 9, 0.31, 8, 10000.0, None, 0, 3, 2, 18)], (0, 2, 2))
 # G: keys of 32 and values of 48, both widened to the 64 the tensor-core attention kernels take (five query heads per
 #    key/value head); then a layer with a key/value head per query head at head size 64; ten experts of 96, three per
 #    row; the middle layers run twice
