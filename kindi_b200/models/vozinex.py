@@ -219,7 +219,10 @@ def build_spec(cfg: VozinexConfig) -> ModelSpec:
         architecture=cfg.architecture, vocab_size=cfg.vocab, width=cfg.width, layers=tuple(layers),
         schedule=tuple(schedule), final_norm=norm, final_norm_prefix=FINAL_NORM,
         embedding=PartSpec("table", {"name": EMBEDDING, "vocab": cfg.vocab}),
-        head=PartSpec("linear", {"name": HEAD, "vocab": cfg.vocab}))
+        head=PartSpec("linear", {"name": HEAD, "vocab": cfg.vocab}),
+        # a layer without a feed-forward has no use for a second norm: a folder that stores one all the same is accepted
+        may_ignore=tuple(n for i, l in enumerate(cfg.layers) if l.mlp is None
+                         for n in ("l%d.norm2" % i, "l%d.norm2.b" % i)))
     spec.validate()
     return spec
 

@@ -31,6 +31,7 @@ def test_config_reads_every_size_from_the_nested_keys():
     assert names["l0.mlp.router"] == (5, 64) and names["l0.mlp.router.b"] == (5,)
     assert names["l2.mlp.e4.up"] == (24, 64) and names["l2.mlp.e4.down"] == (64, 24)
     assert not any(n.startswith("l1.mlp") or n.startswith("l1.norm2") for n in names)
+    assert spec.may_ignore == ("l1.norm2", "l1.norm2.b")       # (a folder may still store the unused norm)
 
 
 @pytest.mark.parametrize("change,word", [
