@@ -103,7 +103,7 @@ def _read_attention(raw: Mapping[str, Any], where: str) -> VozinexAttention:
         raise ConfigError("%s: heads %d is not a multiple of kv_heads %d" % (where, heads, kv))
     dim = _positive(where + ".dim", r.integer("dim"))
     vdim = _positive(where + ".vdim", r.integer("vdim", dim))
-    scale = r.number("scale")
+    scale = r.number("scale", dim ** -0.5)
     if not (scale > 0.0):
         raise ConfigError("%s: scale must be positive, found %r" % (where, scale))
     rot = ConfigReader(r.any("rot") or {}, where + ".rot")
