@@ -104,13 +104,32 @@ __device__ __forceinline__ float4 kb_sum_planes4(float4 v, const float* __restri
     }
     return v;
 }
+// A branch with a per-column scale ("layer scale"): v = x + ls * (sum of the planes, in order). The planes are summed
+// from zero first, so the scale multiplies the whole branch once.
+template <typename TW>
+__device__ __forceinline__ float kb_add_branch(float xv, const float* __restrict__ d, int n, size_t stride,
+                                               const TW* __restrict__ ls, int i) {
+    if (ls == nullptr) return kb_sum_planes(xv, d, n, stride);
+    return __fadd_rn(xv, __fmul_rn(kb_sum_planes(0.0f, d, n, stride), kb_to_f<TW>(ls[i])));
+}
+template <typename TW>
+__device__ __forceinline__ float4 kb_add_branch4(float4 xv, const float* __restrict__ d, int n, size_t stride,
+                                                 const TW* __restrict__ ls, int i) {
+    if (ls == nullptr) return kb_sum_planes4(xv, d, n, stride);
+    const float4 b = kb_sum_planes4(make_float4(0.f, 0.f, 0.f, 0.f), d, n, stride);
+    xv.x = __fadd_rn(xv.x, __fmul_rn(b.x, kb_to_f<TW>(ls[i])));
+    xv.y = __fadd_rn(xv.y, __fmul_rn(b.y, kb_to_f<TW>(ls[i + 1])));
+    xv.z = __fadd_rn(xv.z, __fmul_rn(b.z, kb_to_f<TW>(ls[i + 2])));
+    xv.w = __fadd_rn(xv.w, __fmul_rn(b.w, kb_to_f<TW>(ls[i + 3])));
+    return xv;
+}
 // VEC: the width is a multiple of 4 and every row is 16-byte aligned: a thread takes four neighbouring elements (one
 // pass for widths up to 4096) with all its loads in flight at once. Each element's own sum (residual, then the
 // planes in order) is the same in both forms.
 template <typename TY, typename TW, bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
         int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, TY* __restrict__ y,
-        const int* __restrict__ rows, int T, int E, int write_back, int* status) {
+        const int* __restrict__ rows, int T, int E, int write_back, int* status, const TW* __restrict__ ls) {
     extern __shared__ float sv[];
     __shared__ float red[NORM_THREADS / 32];
     kb_pdl_launch();
@@ -136,7 +155,7 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* KB_STEP_DAT
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < E) {
             v = *(const float4*)(xr + i);
-            if (n_delta > 0) v = kb_sum_planes4(v, dr + i, n_delta, delta_stride);
+            if (n_delta > 0) v = kb_add_branch4<TW>(v, dr + i, n_delta, delta_stride, ls, i);
             if (write_back) *(float4*)(xr + i) = v;
             ss = fmaf(v.x, v.x, ss);
             ss = fmaf(v.y, v.y, ss);
@@ -163,7 +182,7 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* KB_STEP_DAT
     if (VEC) {
         for (int i = threadIdx.x * 4; i < E; i += NORM_THREADS * 4) {
             float4 v = *(const float4*)(xr + i);
-            if (n_delta > 0) v = kb_sum_planes4(v, dr + i, n_delta, delta_stride);
+            if (n_delta > 0) v = kb_add_branch4<TW>(v, dr + i, n_delta, delta_stride, ls, i);
             if (write_back) *(float4*)(xr + i) = v;
             *(float4*)(sv + i) = v;
             ss = fmaf(v.x, v.x, ss);
@@ -174,7 +193,7 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* KB_STEP_DAT
     } else {
         for (int i = threadIdx.x; i < E; i += NORM_THREADS) {
             float v = xr[i];
-            if (n_delta > 0) v = kb_sum_planes(v, dr + i, n_delta, delta_stride);
+            if (n_delta > 0) v = kb_add_branch<TW>(v, dr + i, n_delta, delta_stride, ls, i);
             if (write_back) xr[i] = v;
             sv[i] = v;
             ss = fmaf(v, v, ss);
@@ -198,7 +217,8 @@ __global__ void __launch_bounds__(NORM_THREADS) k_add_rmsnorm(float* KB_STEP_DAT
 // a step has, never uses it.
 template <typename TW>
 __global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
-        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E,
+        const TW* __restrict__ ls) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int t = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -216,7 +236,8 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* KB_STEP_DATA x,
         if (n_delta > 0) {
 #pragma unroll
             for (int u = 0; u < 4; u++)
-                if (i0 + u * 128 < E) v[u] = kb_sum_planes4(v[u], dr + i0 + u * 128, n_delta, delta_stride);
+                if (i0 + u * 128 < E)
+                    v[u] = kb_add_branch4<TW>(v[u], dr + i0 + u * 128, n_delta, delta_stride, ls, i0 + u * 128);
 #pragma unroll
             for (int u = 0; u < 4; u++)
                 if (i0 + u * 128 < E) *(float4*)(xr + i0 + u * 128) = v[u];
@@ -246,18 +267,21 @@ __global__ void __launch_bounds__(256) k_add_rmsnorm_warp(float* KB_STEP_DATA x,
 // in flight before the first sum, and the row is read once. Same sums in the same order as k_add_rmsnorm_warp.
 template <typename TW, int NCH>
 __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
-        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E,
+        const TW* __restrict__ ls) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     float* xr = x + (size_t)t * E;
     const float* dr = delta + (size_t)t * E;
+    // (with a layer scale the planes are summed from zero and the residual comes in after the scale)
+    const bool scaled = ls != nullptr && n_delta > 0;
     float4 v[NCH];
 #pragma unroll
     for (int c = 0; c < NCH; c++) {
         const int i = (c * 32 + lane) * 4;
-        v[c] = i < E ? *(const float4*)(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[c] = (i < E && !scaled) ? *(const float4*)(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     for (int s = 0; s < n_delta; s++) {
         const float* ds = dr + (size_t)s * delta_stride;
@@ -277,6 +301,19 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* KB_STEP_DATA
                     v[c0 + j].z += d[j].z;
                     v[c0 + j].w += d[j].w;
                 }
+        }
+    }
+    if (scaled) {
+#pragma unroll
+        for (int c = 0; c < NCH; c++) {
+            const int i = (c * 32 + lane) * 4;
+            if (i < E) {
+                const float4 xv = *(const float4*)(xr + i);
+                v[c].x = __fadd_rn(xv.x, __fmul_rn(v[c].x, kb_to_f<TW>(ls[i])));
+                v[c].y = __fadd_rn(xv.y, __fmul_rn(v[c].y, kb_to_f<TW>(ls[i + 1])));
+                v[c].z = __fadd_rn(xv.z, __fmul_rn(v[c].z, kb_to_f<TW>(ls[i + 2])));
+                v[c].w = __fadd_rn(xv.w, __fmul_rn(v[c].w, kb_to_f<TW>(ls[i + 3])));
+            }
         }
     }
     float ss = 0.0f;
@@ -315,7 +352,8 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_regs(float* KB_STEP_DATA
 // the four warps' sums of squares are added in warp order.
 template <typename TW, int NC>
 __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_row4(float* KB_STEP_DATA x, const float* KB_STEP_DATA delta,
-        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E) {
+        int n_delta, size_t delta_stride, const TW* __restrict__ w, float eps, bf16* __restrict__ y, int T, int E,
+        const TW* __restrict__ ls) {
     constexpr int PB = 12 / NC > 0 ? 12 / NC : 1;          // planes in flight
     __shared__ float s_ss[8];
     kb_pdl_launch();
@@ -325,11 +363,12 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_row4(float* KB_STEP_DATA
     const bool live = t < T;
     float* xr = x + (size_t)t * E;
     const float* dr = delta + (size_t)t * E;
+    const bool scaled = ls != nullptr && n_delta > 0;
     float4 v[NC];
 #pragma unroll
     for (int c = 0; c < NC; c++) {
         const int i = ((part * NC + c) * 32 + lane) * 4;
-        v[c] = (live && i < E) ? *(const float4*)(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        v[c] = (live && i < E && !scaled) ? *(const float4*)(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     for (int s0 = 0; s0 < n_delta; s0 += PB) {
         float4 d[PB][NC];
@@ -352,6 +391,19 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_row4(float* KB_STEP_DATA
                     v[c].w += d[k][c].w;
                 }
             }
+    }
+    if (scaled && live) {
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            const int i = ((part * NC + c) * 32 + lane) * 4;
+            if (i < E) {
+                const float4 xv = *(const float4*)(xr + i);
+                v[c].x = __fadd_rn(xv.x, __fmul_rn(v[c].x, kb_to_f<TW>(ls[i])));
+                v[c].y = __fadd_rn(xv.y, __fmul_rn(v[c].y, kb_to_f<TW>(ls[i + 1])));
+                v[c].z = __fadd_rn(xv.z, __fmul_rn(v[c].z, kb_to_f<TW>(ls[i + 2])));
+                v[c].w = __fadd_rn(xv.w, __fmul_rn(v[c].w, kb_to_f<TW>(ls[i + 3])));
+            }
+        }
     }
     float ss = 0.0f;
 #pragma unroll
@@ -395,7 +447,9 @@ __global__ void __launch_bounds__(256, 2) k_add_rmsnorm_row4(float* KB_STEP_DATA
 
 extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long long delta_stride, const void* w,
                               int wdtype, float eps, void* y, int ydtype, const int* rows, int n_out, int T, int E,
-                              int write_back, int* status, cudaStream_t st) {
+                              int write_back, int* status, cudaStream_t st, const void* ls) {
+    // ls (the gains' type, E elements, or null): the branch (the sum of the planes) is multiplied by it column by
+    // column before it is added to the residual
     if (n_out <= 0) return 0;
     size_t sm = (size_t)E * sizeof(float);
     if (E > NORM_MAX_E) return (int)cudaErrorInvalidValue;
@@ -408,10 +462,10 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
     do {                                                                                                           \
         if (wdtype == KB_F32)                                                                                      \
             e = kb_launch(k_add_rmsnorm_row4<float, NC>, (T + 1) / 2, 256, 0, st, x, delta, n_delta,               \
-                          (size_t)delta_stride, (const float*)w, eps, (bf16*)y, T, E);                             \
+                          (size_t)delta_stride, (const float*)w, eps, (bf16*)y, T, E, (const float*)ls);            \
         else                                                                                                       \
             e = kb_launch(k_add_rmsnorm_row4<bf16, NC>, (T + 1) / 2, 256, 0, st, x, delta, n_delta,                \
-                          (size_t)delta_stride, (const bf16*)w, eps, (bf16*)y, T, E);                              \
+                          (size_t)delta_stride, (const bf16*)w, eps, (bf16*)y, T, E, (const bf16*)ls);              \
         return (int)e;                                                                                             \
     } while (0)
         if (E <= 4 * 2 * 128) KB_NORM_ROW4(2);
@@ -430,10 +484,10 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
     do {                                                                                                           \
         if (wdtype == KB_F32)                                                                                      \
             e = kb_launch(k_add_rmsnorm_regs<float, NCH>, (T + NORM_RW - 1) / NORM_RW, 32 * NORM_RW, 0, st, x, delta, n_delta, \
-                          (size_t)delta_stride, (const float*)w, eps, (bf16*)y, T, E);                             \
+                          (size_t)delta_stride, (const float*)w, eps, (bf16*)y, T, E, (const float*)ls);            \
         else                                                                                                       \
             e = kb_launch(k_add_rmsnorm_regs<bf16, NCH>, (T + NORM_RW - 1) / NORM_RW, 32 * NORM_RW, 0, st, x, delta, n_delta, \
-                          (size_t)delta_stride, (const bf16*)w, eps, (bf16*)y, T, E);                              \
+                          (size_t)delta_stride, (const bf16*)w, eps, (bf16*)y, T, E, (const bf16*)ls);              \
         return (int)e;                                                                                             \
     } while (0)
         if (E <= 8 * 128) KB_NORM_REGS(8);
@@ -442,10 +496,10 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
 #undef KB_NORM_REGS
         if (wdtype == KB_F32)
             e = kb_launch(k_add_rmsnorm_warp<float>, (T + 7) / 8, 256, 0, st, x, delta, n_delta, (size_t)delta_stride,
-                          (const float*)w, eps, (bf16*)y, T, E);
+                          (const float*)w, eps, (bf16*)y, T, E, (const float*)ls);
         else
             e = kb_launch(k_add_rmsnorm_warp<bf16>, (T + 7) / 8, 256, 0, st, x, delta, n_delta, (size_t)delta_stride,
-                          (const bf16*)w, eps, (bf16*)y, T, E);
+                          (const bf16*)w, eps, (bf16*)y, T, E, (const bf16*)ls);
         return (int)e;
     }
 #define KB_NORM1(TY, TW, V)                                                                                      \
@@ -453,7 +507,8 @@ extern "C" int kb_add_rmsnorm(float* x, const float* delta, int n_delta, long lo
         if (sm > 48 * 1024)                                                                                      \
             cudaFuncSetAttribute(k_add_rmsnorm<TY, TW, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); \
         e = kb_launch(k_add_rmsnorm<TY, TW, V>, n_out, NORM_THREADS, sm, st, x, delta, n_delta,                  \
-                      (size_t)delta_stride, (const TW*)w, eps, (TY*)y, rows, T, E, write_back, status);          \
+                      (size_t)delta_stride, (const TW*)w, eps, (TY*)y, rows, T, E, write_back, status,            \
+                      (const TW*)ls);                                                                            \
     } while (0)
 #define KB_NORM(TY, TW)                \
     do {                               \
@@ -971,11 +1026,12 @@ extern "C" int kb_rope_store(const void* in, int in_dtype, int n_planes, long lo
 // from the cache. Keys are taken in runs of 32 that start at multiples of 32 of the absolute
 // position (lane = position for the scores, lane = dimension for P V) with a running maximum and sum, so the order
 // of every sum depends on positions only: the same row gives the same bits whether it came in a prompt or alone.
-#define AG_MAX_HD 256
+#define AG_MAX_HD 512
 template <typename T>
 __global__ void __launch_bounds__(128) k_attn_generic(const T* KB_STEP_DATA q, int ldq, T* __restrict__ out,
         int ldo, const int* __restrict__ pos, const int* __restrict__ seq, const int* __restrict__ slot, int Tn,
-        int nh, int group, int hd, float scale, int window, int keep_first, KbCacheView cv, int* status) {
+        int nh, int group, int hd, float scale, int window, int keep_first, KbCacheView cv, int* status,
+        const float* __restrict__ sink, const T* KB_STEP_DATA gate, int ldg) {
     __shared__ float qs[4][AG_MAX_HD];
     kb_pdl_launch();
     kb_pdl_wait();
@@ -1038,18 +1094,35 @@ __global__ void __launch_bounds__(128) k_attn_generic(const T* KB_STEP_DATA q, i
             }
         }
     }
+    if (sink != nullptr) {
+        // a learned score per head that has no key and no value: it counts once in the denominator, unscaled
+        const float sk = sink[h];
+        const float mn = fmaxf(m, sk);
+        const float f = expf(m - mn);
+        l = l * f + expf(sk - mn);
+#pragma unroll
+        for (int i = 0; i < AG_MAX_HD / 32; i++) o[i] *= f;
+    }
     T* orow = out + (size_t)t * ldo + (size_t)h * hd;
+    const T* grow = gate ? gate + (size_t)t * ldg + (size_t)h * hd : nullptr;
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; i++) {
         const int d = i * 32 + lane;
-        if (d < hd) orow[d] = kb_from_f<T>(o[i] / l);
+        if (d < hd) {
+            float v = o[i] / l;
+            // an output gate: the head's output times the logistic function of the gate's row
+            if (grow) v = v * (1.0f / (1.0f + expf(-kb_to_f<T>(grow[d]))));
+            orow[d] = kb_from_f<T>(v);
+        }
     }
 }
 
 extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int ldo, const int* pos, const int* seq,
                                const int* slot, int T, int nh, int nkv, int hd, float scale, int window, void* pool,
                                const int* table, int table_stride, int n_pages, int* status, cudaStream_t st,
-                               int keep_first) {
+                               int keep_first, const float* sink, const void* gate, int ldg) {
+    // sink (float [nh] or null): exp(sink[h]) joins the softmax denominator of head h. gate (rows of the queries'
+    // type [T][ldg], laid out like the output, or null): out *= 1 / (1 + exp(-gate))
     if (T <= 0) return 0;
     if (hd > AG_MAX_HD || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
     if (window <= 0 || keep_first < 0) keep_first = 0;
@@ -1058,18 +1131,28 @@ extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int
     int grid = (int)((items + 3) / 4);
     if (dtype == KB_F32)
         kb_launch(k_attn_generic<float>, grid, 128, 0, st, (const float*)q, ldq, (float*)out, ldo, pos, seq, slot, T, nh,
-                                                   nh / nkv, hd, scale, window, keep_first, cv, status);
+                                                   nh / nkv, hd, scale, window, keep_first, cv, status, sink, (const float*)gate, ldg);
     else
         kb_launch(k_attn_generic<bf16>, grid, 128, 0, st, (const bf16*)q, ldq, (bf16*)out, ldo, pos, seq, slot, T, nh,
-                                                  nh / nkv, hd, scale, window, keep_first, cv, status);
+                                                  nh / nkv, hd, scale, window, keep_first, cv, status, sink, (const bf16*)gate, ldg);
     KB_LAUNCH_RET();
 }
 
 // ------------------------------------------------------------------------------------------------ SwiGLU
+// the gate's activation is a parameter (KB_ACT_SILU, or KB_ACT_GELU_TANH for a gated feed-forward with the tanh form
+// of GELU); kb_gate_act is exact, kb_gate_act_fast uses the fast exponential and division, whose error is far below
+// one bf16 rounding: gelu_tanh(z) = z / (1 + exp(-2 u)) with u = sqrt(2 / pi) (z + 0.044715 z^3)
+__device__ __forceinline__ float kb_gate_act(float g, int act) {
+    return act == KB_ACT_GELU_TANH ? kb_act(g, KB_ACT_GELU_TANH) : g / (1.0f + expf(-g));
+}
+__device__ __forceinline__ float kb_gate_act_fast(float g, int act) {
+    const float e = act == KB_ACT_GELU_TANH ? -1.5957691216057308f * (g + 0.044715f * g * g * g) : -g;
+    return __fdividef(g, 1.0f + __expf(e));
+}
 // gu: [T][2F] = gate then up; out[t][i] = gate / (1 + exp(-gate)) * up (kindi/nbq.cu:461-467)
 template <typename TIN, typename T>
 __global__ void k_swiglu(const TIN* KB_STEP_DATA gu, int n_planes, size_t plane_stride, T* __restrict__ out, int F,
-                         long long total, int group) {
+                         long long total, int group, int act) {
     kb_pdl_launch();
     kb_pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1093,13 +1176,13 @@ __global__ void k_swiglu(const TIN* KB_STEP_DATA gu, int n_planes, size_t plane_
                 u += tu[j];
             }
     }
-    out[i] = kb_from_f<T>(g / (1.0f + expf(-g)) * u);
+    out[i] = kb_from_f<T>(kb_gate_act(g, act) * u);
 }
 
 // the same with a row per blockIdx.y and two neighbouring columns per thread (F even, aligned rows)
 template <typename TIN, typename T>
 __global__ void __launch_bounds__(256) k_swiglu2(const TIN* KB_STEP_DATA gu, int n_planes, size_t plane_stride,
-                                                  T* __restrict__ out, int F, int group) {
+                                                  T* __restrict__ out, int F, int group, int act) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int c = (blockIdx.x * 256 + threadIdx.x) * 2;
@@ -1124,13 +1207,13 @@ __global__ void __launch_bounds__(256) k_swiglu2(const TIN* KB_STEP_DATA gu, int
                 u.y += tu[j].y;
             }
     }
-    kb_st2(out + t * F + c, make_float2(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y));
+    kb_st2(out + t * F + c, make_float2(kb_gate_act(g.x, act) * u.x, kb_gate_act(g.y, act) * u.y));
 }
 
 // bf16 rows in, bf16 out, eight columns per thread with 16-byte accesses; exp and the division by the fast
 // intrinsics (their error is far below one bf16 rounding)
 __global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* KB_STEP_DATA gu, bf16* __restrict__ out, int F,
-                                                      int group) {
+                                                      int group, int act) {
     kb_pdl_launch();
     kb_pdl_wait();
     const int c = (blockIdx.x * 256 + threadIdx.x) * 8;
@@ -1145,8 +1228,7 @@ __global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* KB_STEP_DATA g
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-        o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x,
-                                      __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y);
+        o2[j] = __floats2bfloat162_rn(kb_gate_act_fast(g.x, act) * u.x, kb_gate_act_fast(g.y, act) * u.y);
     }
     *(uint4*)(out + t * F + c) = ov;
 }
@@ -1154,8 +1236,9 @@ __global__ void __launch_bounds__(256) k_swiglu8_bf16(const bf16* KB_STEP_DATA g
 // gu: [n_planes][T][2F] (planes summed in order), 32-bit or the output's type. Columns come in groups: `group` gate
 // columns, then the `group` up columns of the same outputs (group == F: all gates, then all ups).
 extern "C" int kb_swiglu(const void* gu, int in_dtype, int n_planes, long long plane_stride, void* out, int dtype,
-                         int T, int F, int group, cudaStream_t st) {
+                         int T, int F, int group, cudaStream_t st, int act) {
     if (group <= 0 || F % group) return (int)cudaErrorInvalidValue;
+    if (act != KB_ACT_GELU_TANH) act = KB_ACT_SILU;
     long long total = (long long)T * F;
     if (total <= 0) return 0;
     int grid = (int)((total + 255) / 256);
@@ -1163,27 +1246,27 @@ extern "C" int kb_swiglu(const void* gu, int in_dtype, int n_planes, long long p
     if (in_dtype == KB_BF16 && dtype == KB_BF16 && n_planes == 1 && F % 8 == 0 && group % 8 == 0 && ((uintptr_t)gu % 16) == 0 &&
         ((uintptr_t)out % 16) == 0 && T <= 65535) {
         dim3 g8((F / 8 + 255) / 256, T);
-        kb_launch(k_swiglu8_bf16, g8, 256, 0, st, (const bf16*)gu, (bf16*)out, F, group);
+        kb_launch(k_swiglu8_bf16, g8, 256, 0, st, (const bf16*)gu, (bf16*)out, F, group, act);
         KB_LAUNCH_RET();
     }
     if (F % 2 == 0 && group % 2 == 0 && plane_stride % 2 == 0 && ((uintptr_t)gu % (2 * in_el)) == 0 &&
         ((uintptr_t)out % (2 * out_el)) == 0 && T <= 65535) {
         dim3 g2((F / 2 + 255) / 256, T);
         if (in_dtype == KB_F32 && dtype == KB_F32)
-            kb_launch(k_swiglu2<float, float>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, group);
+            kb_launch(k_swiglu2<float, float>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, group, act);
         else if (in_dtype == KB_F32 && dtype == KB_BF16)
-            kb_launch(k_swiglu2<float, bf16>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, group);
+            kb_launch(k_swiglu2<float, bf16>, g2, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, group, act);
         else if (in_dtype == KB_BF16 && dtype == KB_BF16)
-            kb_launch(k_swiglu2<bf16, bf16>, g2, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, group);
+            kb_launch(k_swiglu2<bf16, bf16>, g2, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, group, act);
         else return (int)cudaErrorInvalidValue;
         KB_LAUNCH_RET();
     }
     if (in_dtype == KB_F32 && dtype == KB_F32)
-        kb_launch(k_swiglu<float, float>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total, group);
+        kb_launch(k_swiglu<float, float>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (float*)out, F, total, group, act);
     else if (in_dtype == KB_F32 && dtype == KB_BF16)
-        kb_launch(k_swiglu<float, bf16>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total, group);
+        kb_launch(k_swiglu<float, bf16>, grid, 256, 0, st, (const float*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total, group, act);
     else if (in_dtype == KB_BF16 && dtype == KB_BF16)
-        kb_launch(k_swiglu<bf16, bf16>, grid, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total, group);
+        kb_launch(k_swiglu<bf16, bf16>, grid, 256, 0, st, (const bf16*)gu, n_planes, (size_t)plane_stride, (bf16*)out, F, total, group, act);
     else return (int)cudaErrorInvalidValue;
     KB_LAUNCH_RET();
 }

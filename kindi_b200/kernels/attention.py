@@ -4,16 +4,21 @@ from __future__ import annotations
 from . import lib as K
 
 
-def attention(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0) -> None:
+def attention(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0, sink=None,
+              gate=None) -> bool:
     """``out`` = attention of the (already position-encoded) query rows ``q`` over their sequences' cached keys and
     values, which include this step's: all positions up to the row's, or with ``window`` the last ``window`` of them
-    and the sequence's first ``keep_first``"""
+    and the sequence's first ``keep_first``. ``sink`` (float32 ``[nh]``): ``exp(sink_h)`` joins head h's softmax
+    denominator. ``gate`` (rows or 32-bit planes laid out like ``out``): an output gate ``out *= sigmoid(gate)``; the
+    return value says whether the kernel applied it (False: the caller still has to)"""
     if ctx.fast:
         from . import fast
-        if fast.attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first):
-            return
+        if fast.attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first, sink):
+            return False
+    rows_gate = gate if gate is not None and gate.dim() == 2 and gate.dtype == q.dtype else None
     K.attn_generic(q, out, ctx.pos, ctx.seq, ctx.slot, nh, nkv, hd, scale, window, pool, table, n_pages, ctx.status,
-                   keep_first)
+                   keep_first, sink, rows_gate)
+    return rows_gate is not None
 
 
 def attention_from_planes(ctx, qkv, out, nh, nkv, hd, scale, window, rotation, pool, table, n_pages) -> bool:

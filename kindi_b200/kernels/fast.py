@@ -182,10 +182,13 @@ def gemm_planes(a: torch.Tensor, w: torch.Tensor, status: torch.Tensor) -> Optio
     return out
 
 
-def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
+def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+                     act: str = "silu") -> bool:
     """out (bf16 [M, F]) = silu(g) * u for a prompt-sized step, finished inside the product's epilogue; w_grouped
     [2F, K] holds 16 gate rows then the 16 up rows of the same outputs, group after group. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
+    if act != "silu":
+        return False
     if _swiglu_in_decode_form(a) or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
         return False
     _prefill_product(a, w_grouped, out, status, True)
@@ -210,10 +213,13 @@ def reset_scratch() -> None:
         flags.zero_()
 
 
-def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
+def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+                       act: str = "silu") -> bool:
     """out (bf16 [M, F]) = silu(g) * u for a decode-sized step, finished inside the product (no split-K planes, no
     SwiGLU kernel); w_grouped [2F, K] as for gemm_swiglu_rows. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
+    if act != "silu":
+        return False
     if not _swiglu_in_decode_form(a) or not _tc_ok(a, w_grouped) or n % 32 or out.stride(1) != 1 \
             or out.dtype != torch.bfloat16:
         return False
@@ -228,8 +234,11 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
     return True
 
 
-def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0) -> bool:
+def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0,
+                   sink=None) -> bool:
     """the tensor-core attention kernel, where it takes the shape: head size 64 or 128, bf16, aligned rows"""
+    if sink is not None:
+        return False
     if hd not in (64, 128) or q.dtype != torch.bfloat16 or q.stride(0) % 8 or q.data_ptr() % 16:
         return False
     g = nh // nkv

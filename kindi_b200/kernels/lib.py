@@ -32,7 +32,7 @@ _SIGS = {
     "kb_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "kb_logit_post": [c_void_p, c_longlong, c_float, c_float, c_void_p],
     "kb_add_rmsnorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p,
-                       c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                       c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "kb_gemm_simt": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                      c_void_p],
     "kb_rope_store": [c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
@@ -40,7 +40,21 @@ _SIGS = {
                       c_void_p, c_void_p],
     "kb_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "kb_attn_generic": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                        c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int],
+                        c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                        c_void_p, c_int],
+    "kb_gate_mul": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int, c_int, c_int,
+                    c_void_p],
+    "kb_gated_rmsnorm": [c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p,
+                         c_int, c_int, c_int, c_int, c_void_p],
+    "kb_latent_prep": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                       c_float, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                       c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    "kb_latent_qrope": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                        c_int, c_int, c_int, c_void_p],
+    "kb_head_gemm": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p],
+    "kb_decay_scan": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "kb_add_layernorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int,
                          c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_residual_add": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_void_p],
@@ -57,7 +71,7 @@ _SIGS = {
     "kb_moe_gather": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     "kb_moe_gemm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int,
                     c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "kb_swiglu": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int],
     "kb_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                    c_longlong, c_void_p, c_void_p, c_int, c_int],
     "kb_gemm_tc_splits": [c_int, c_int],
@@ -256,9 +270,13 @@ def logit_post(logits: torch.Tensor, scale: float = 1.0, softcap: float = 0.0) -
 
 
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float, out: torch.Tensor,
-                rows: Optional[torch.Tensor], write_back: bool, status: torch.Tensor) -> None:
-    """x (float32 [T, E]) + sum of delta ([S, T, E] float32) -> RMS norm * w -> out ([R, E]); rows int32 or None"""
-    _need_cuda(x, delta, w, out, rows)
+                rows: Optional[torch.Tensor], write_back: bool, status: torch.Tensor,
+                branch_scale: Optional[torch.Tensor] = None) -> None:
+    """x (float32 [T, E]) + sum of delta ([S, T, E] float32) -> RMS norm * w -> out ([R, E]); rows int32 or None.
+    ``branch_scale`` ([E], the gains' dtype): the summed delta is multiplied by it, column by column, before the add"""
+    _need_cuda(x, delta, w, out, rows, branch_scale)
+    if branch_scale is not None:
+        assert branch_scale.dtype == w.dtype and branch_scale.is_contiguous() and branch_scale.numel() == x.shape[1]
     T, E = x.shape
     n_out = out.shape[0]
     assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and w.shape == (E,)
@@ -273,7 +291,8 @@ def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor,
     if E * 4 > 200 * 1024:
         raise KernelError("kindi_b200: RMS norm supports a width up to 51200, found %d" % E)
     _check(load().kb_add_rmsnorm(_p(x), _p(delta), nd, stride, _p(w), dt(w), float(eps), _p(out), dt(out), _p(rows),
-                                 n_out, T, E, 1 if write_back else 0, _p(status), _stream()), "add_rmsnorm")
+                                 n_out, T, E, 1 if write_back else 0, _p(status), _stream(),
+                                 _p(branch_scale) if delta is not None else None), "add_rmsnorm")
 
 
 def add_layernorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, b: torch.Tensor, eps: float,
@@ -341,6 +360,107 @@ def norm_rope_store(qkv: torch.Tensor, qout: torch.Tensor, wq: Optional[torch.Te
 
 
 ACT = {"none": 0, "relu2": 1, "silu": 2, "gelu_tanh": 3}
+GATE_ACT = {"silu": ACT["silu"], "gelu_tanh": ACT["gelu_tanh"]}      # what a gated feed-forward's gate may pass through
+
+
+def _planes_of(g: torch.Tensor):
+    """(number of planes, plane stride, row stride) of rows [T, N] or 32-bit planes [S, T, N]"""
+    if g.dim() == 3:
+        assert g.dtype == torch.float32 and g.stride(2) == 1
+        return g.shape[0], g.stride(0), g.stride(1)
+    assert g.stride(1) == 1
+    return 1, 0, g.stride(0)
+
+
+def gate_mul(a: torch.Tensor, g: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t][c] = a[t][c] * sigmoid(g[t][c]); ``g``: rows [T, N] or 32-bit planes [S, T, N] (views are fine)"""
+    _need_cuda(a, g, out)
+    T, N = a.shape
+    n_planes, pstride, ldg = _planes_of(g)
+    assert g.shape[-2:] == (T, N) and out.shape == (T, N) and a.stride(1) == 1 and out.stride(1) == 1
+    assert out.dtype == a.dtype
+    _check(load().kb_gate_mul(_p(a), dt(a), a.stride(0), _p(g), dt(g), n_planes, pstride, ldg, _p(out), out.stride(0),
+                              T, N, _stream()), "gate_mul")
+
+
+def gated_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, g: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w * sigmoid(g[t]); x float32 [T, N]; ``g`` rows or 32-bit planes"""
+    _need_cuda(x, w, g, out)
+    T, N = x.shape
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and w.numel() == N and w.is_contiguous()
+    assert out.shape == (T, N) and out.stride(1) == 1
+    n_planes, pstride, ldg = _planes_of(g) if g is not None else (1, 0, 0)
+    if g is not None:
+        assert g.shape[-2:] == (T, N)
+    _check(load().kb_gated_rmsnorm(_p(x), x.stride(0), _p(w), dt(w), float(eps), _p(g), dt(g) if g is not None else F32,
+                                   n_planes, pstride, ldg, _p(out), dt(out), out.stride(0), T, N, _stream()),
+           "gated_rmsnorm")
+
+
+def latent_prep(a: torch.Tensor, q_rank: int, kv_rank: int, rot: int, wq: torch.Tensor, wkv: torch.Tensor, eps: float,
+                freq: torch.Tensor, mult: float, pos, seq, slot, cq: torch.Tensor, head_dim: int, pool: torch.Tensor,
+                table: torch.Tensor, n_pages: int, status: torch.Tensor) -> None:
+    """``a``: rows or 32-bit planes of [query latent | key/value latent | rotated key part | ...]. Writes the RMS-normed
+    query latent to ``cq`` and stores, at each row's position of its sequence's pages, one key head [normed latent |
+    rotated part | 0] and one value head [normed latent | 0] of ``head_dim`` elements. The rotation pairs element 2i
+    with 2i + 1, by pos * freq[i], cosine and sine times ``mult``"""
+    _need_cuda(a, wq, wkv, freq, cq, pool, table)
+    n_planes, pstride, ld = _planes_of(a)
+    T = a.shape[-2]
+    assert a.shape[-1] >= q_rank + kv_rank + rot and wq.dtype == wkv.dtype and wq.numel() == q_rank
+    assert wkv.numel() == kv_rank and wq.is_contiguous() and wkv.is_contiguous()
+    assert freq.dtype == torch.float32 and freq.numel() >= max(1, rot // 2) and freq.is_contiguous()
+    assert cq.shape == (T, q_rank) and cq.stride(1) == 1 and pool.dtype == cq.dtype and pool.is_contiguous()
+    assert pool.shape[-1] == head_dim and pool.shape[-3] == 1
+    _check(load().kb_latent_prep(_p(a), dt(a), n_planes, pstride, ld, q_rank, kv_rank, rot, _p(wq), _p(wkv), dt(wq),
+                                 float(eps), _p(freq), float(mult), _p(pos), _p(seq), _p(slot), _p(cq), dt(cq),
+                                 cq.stride(0), T, head_dim, _p(pool), _p(table), table.stride(0), n_pages, _p(status),
+                                 _stream()), "latent_prep")
+
+
+def latent_qrope(q: torch.Tensor, dim: int, rot: int, freq: torch.Tensor, mult: float, pos, out: torch.Tensor,
+                 at: int, head_dim: int, n_heads: int) -> None:
+    """q rows [T, n_heads (dim + rot)]: each head's last ``rot`` elements, rotated (pairs 2i, 2i + 1), go to
+    out[t][h][at : at + rot]; out[t][h][at + rot : head_dim] = 0"""
+    _need_cuda(q, freq, out)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype and q.shape[1] == n_heads * (dim + rot)
+    assert out.shape == (T, n_heads * head_dim) and freq.dtype == torch.float32
+    _check(load().kb_latent_qrope(_p(q), dt(q), q.stride(0), dim, rot, _p(freq), float(mult), _p(pos), _p(out),
+                                  out.stride(0), at, head_dim, T, n_heads, _stream()), "latent_qrope")
+
+
+def head_gemm(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int,
+              gate: Optional[torch.Tensor] = None) -> None:
+    """per head h: out[t][h * out_head_stride + n] = sum_k a[t][h * a_head_stride + k] * w[h][n][k]; w [H, N, K].
+    ``gate`` (rows or 32-bit planes [.., T, H * N]): the result is multiplied by its logistic function"""
+    _need_cuda(a, w, out, gate)
+    H, N, Kd = w.shape
+    M = a.shape[0]
+    assert a.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous() and out.dtype == a.dtype
+    assert a.shape[1] >= (H - 1) * a_head_stride + Kd and out.shape[1] >= (H - 1) * out_head_stride + N
+    n_planes, pstride, ldg = _planes_of(gate) if gate is not None else (1, 0, 0)
+    if gate is not None:
+        assert gate.shape[-2:] == (M, H * N)
+    _check(load().kb_head_gemm(_p(a), dt(a), a.stride(0), a_head_stride, _p(w), dt(w), _p(out), out.stride(0),
+                               out_head_stride, M, N, Kd, H, _p(gate), dt(gate) if gate is not None else F32, n_planes,
+                               pstride, ldg, _stream()), "head_gemm")
+
+
+def decay_scan(a: torch.Tensor, B: int, H: int, d: int, dv: int, decay: torch.Tensor, q_start, slot,
+               state: torch.Tensor, out: torch.Tensor) -> None:
+    """linear attention with a decay per head over the packed rows of ``B`` sequences: ``a`` rows or 32-bit planes of
+    [q (H d) | k (H d) | v (H dv) | ...] (silu is applied here); ``state`` float32 [slots, H, dv, d] is read and
+    written; ``out`` float32 [T, H dv]"""
+    _need_cuda(a, decay, state, out)
+    n_planes, pstride, ld = _planes_of(a)
+    assert a.shape[-1] >= 2 * H * d + H * dv and decay.dtype == torch.float32 and decay.numel() == H
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (H, dv, d)
+    assert out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == H * dv
+    if d > 256:
+        raise KernelError("kindi_b200: linear attention supports key sizes up to 256, found %d" % d)
+    _check(load().kb_decay_scan(_p(a), dt(a), n_planes, pstride, ld, B, H, d, dv, _p(decay), _p(q_start), _p(slot),
+                                _p(state), _p(out), out.stride(0), _stream()), "decay_scan")
 
 
 def moe_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
@@ -515,29 +635,36 @@ def rope_store(qkv: torch.Tensor, qout: torch.Tensor, inv_freq: torch.Tensor, ro
 
 def attn_generic(q: torch.Tensor, out: torch.Tensor, pos, seq, slot, nh: int, nkv: int, hd: int, scale: float,
                  window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, status: torch.Tensor,
-                 keep_first: int = 0) -> None:
+                 keep_first: int = 0, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """attention of each row of q ([T, >= nh hd], row stride free) over its sequence's cached keys and values: all
-    positions up to the row's, or with ``window`` the last ``window`` of them and the sequence's first ``keep_first``"""
-    _need_cuda(q, out, pool, table)
+    positions up to the row's, or with ``window`` the last ``window`` of them and the sequence's first ``keep_first``.
+    ``sink`` (float32 [nh]): exp(sink[h]) joins head h's softmax denominator. ``gate`` (rows of q's dtype, laid out
+    like ``out``): the output is multiplied by the logistic function of it"""
+    _need_cuda(q, out, pool, table, sink, gate)
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh
+    if gate is not None:
+        assert gate.dtype == q.dtype and gate.stride(1) == 1 and gate.shape[0] == q.shape[0]
     T = q.shape[0]
-    if hd > 256:
-        raise KernelError("kindi_b200: attention supports head sizes up to 256, found %d" % hd)
+    if hd > 512:
+        raise KernelError("kindi_b200: attention supports head sizes up to 512, found %d" % hd)
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == pool.dtype
     _check(load().kb_attn_generic(_p(q), dt(q), q.stride(0), _p(out), out.stride(0), _p(pos), _p(seq), _p(slot), T,
                                   nh, nkv, hd, float(scale), int(window), _p(pool), _p(table), table.stride(0),
-                                  n_pages, _p(status), _stream(), int(keep_first)), "attn_generic")
+                                  n_pages, _p(status), _stream(), int(keep_first), _p(sink), _p(gate),
+                                  gate.stride(0) if gate is not None else 0), "attn_generic")
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0) -> None:
-    """out[T, F] = silu(g) * u with gu [T, 2F] (or the sum of 32-bit planes gu [S, T, 2F]). The columns of gu come in
+def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0, act: str = "silu") -> None:
+    """out[T, F] = act(g) * u with gu [T, 2F] (or the sum of 32-bit planes gu [S, T, 2F]). The columns of gu come in
     groups of ``group`` gate columns followed by the ``group`` up columns of the same outputs (0: all gates, then
-    all ups)"""
+    all ups). ``act``: "silu" or "gelu_tanh"."""
     _need_cuda(gu, out)
     T, F = out.shape
     planes = gu.shape[0] if gu.dim() == 3 else 1
     assert gu.shape[-2:] == (T, 2 * F) and gu.is_contiguous() and out.is_contiguous()
-    _check(load().kb_swiglu(_p(gu), dt(gu), planes, T * 2 * F, _p(out), dt(out), T, F, group or F, _stream()),
-           "swiglu")
+    _check(load().kb_swiglu(_p(gu), dt(gu), planes, T * 2 * F, _p(out), dt(out), T, F, group or F, _stream(),
+                            GATE_ACT[act]), "swiglu")
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,

@@ -61,13 +61,15 @@ def join_gate_up(gate: torch.Tensor, up: torch.Tensor):
     return joined.contiguous(), group
 
 
-def gate_up_swiglu(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: int, out_dtype: torch.dtype) -> torch.Tensor:
-    """``silu(g) * u`` (``[M, F]`` in out_dtype) with ``[g | u] = y @ wgu^T``, ``wgu`` as ``join_gate_up`` made it:
-    inside the product where a tensor-core kernel takes the shape, else the product followed by the SwiGLU kernel"""
+def gate_up_swiglu(ctx, y: torch.Tensor, wgu: torch.Tensor, group: int, f: int, out_dtype: torch.dtype,
+                   act: str = "silu") -> torch.Tensor:
+    """``act(g) * u`` (``[M, F]`` in out_dtype; ``act`` silu or gelu_tanh) with ``[g | u] = y @ wgu^T``, ``wgu`` as
+    ``join_gate_up`` made it: inside the product where a tensor-core kernel takes the shape, else the product followed
+    by the SwiGLU kernel"""
     h = torch.empty((y.shape[0], f), dtype=out_dtype, device=y.device)
-    if ctx.fast and group == GATE_UP_GROUP and (fast.gemm_swiglu_decode(y, wgu, h, ctx.status)
-                                                or fast.gemm_swiglu_rows(y, wgu, h, ctx.status)):
+    if ctx.fast and group == GATE_UP_GROUP and (fast.gemm_swiglu_decode(y, wgu, h, ctx.status, act)
+                                                or fast.gemm_swiglu_rows(y, wgu, h, ctx.status, act)):
         return h
     gu = rows_or_planes(ctx, y, wgu, out_dtype)
-    K.swiglu(gu, h, group)
+    K.swiglu(gu, h, group, act)
     return h

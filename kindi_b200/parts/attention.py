@@ -18,6 +18,12 @@ Options a spec may give:
   by their root mean square over the WHOLE projection (all heads at once) and multiplied by the gains named ``q``
   and ``k`` (one per element of the projection).
 * ``names``: the tensors' suffixes (``q``, ``k``, ``v``, ``o``).
+* ``sink`` (a tensor suffix, ``[n_heads]``): a learned score per head that joins the softmax denominator as
+  ``exp(sink_h)``; it has no key and no value and is not scaled.
+* ``gate`` (a tensor suffix, ``[n_heads * v_head_dim, width]``): the concatenated heads are multiplied by
+  ``sigmoid(W_g y)`` before the output projection; the gate's projection rides in the QKV product.
+* ``shares_kv``: the layer has no key and value projections (no tensors for them); its schedule entry names the cache
+  entry whose keys and values it attends to (``reads_cache_of``).
 """
 from __future__ import annotations
 
@@ -29,6 +35,7 @@ import torch
 from ..config.registry import part_class, register_part
 from ..config.spec import PartSpec
 from ..kernels import attention as A
+from ..kernels import lib as K
 from ..kernels import linear as L
 from .base import Branch, KVNeed, Mixer, StepContext, WeightView
 
@@ -74,8 +81,14 @@ class CausalSelfAttention(Mixer):
         nh, nkv, hd = cls._sizes(spec)
         vd = cls._v_dim(spec)
         n = cls._names(spec)
-        out = {n["q"]: (nh * hd, width), n["k"]: (nkv * hd, width), n["v"]: (nkv * vd, width),
-               n["o"]: (width, nh * vd)}
+        out = {n["q"]: (nh * hd, width), n["o"]: (width, nh * vd)}
+        if not spec.get("shares_kv"):
+            out[n["k"]] = (nkv * hd, width)
+            out[n["v"]] = (nkv * vd, width)
+        if spec.get("sink"):
+            out[spec["sink"]] = (nh,)
+        if spec.get("gate"):
+            out[spec["gate"]] = (nh * vd, width)
         qkn = spec.get("qk_norm")
         if qkn:
             out[qkn["q"]] = (nh * hd,)
@@ -91,7 +104,11 @@ class CausalSelfAttention(Mixer):
     def cache_need(cls, spec: PartSpec, width: int):
         nh, nkv, hd = cls._sizes(spec)
         window = spec.get("window")
-        return KVNeed(nkv, cls._cache_dim(spec), window, int(spec.get("keep_first") or 0) if window else 0)
+        # (``cache_window``: what the cache keeps when other layers with other windows read this layer's keys and
+        # values; "all": every position)
+        kept = spec.get("cache_window")
+        kept = window if kept is None else None if kept == "all" else kept
+        return KVNeed(nkv, cls._cache_dim(spec), kept, int(spec.get("keep_first") or 0) if window and kept else 0)
 
     def __init__(self, spec, width, weights: WeightView, *, dtype, device):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
@@ -100,8 +117,8 @@ class CausalSelfAttention(Mixer):
         self.hd = self._cache_dim(spec)
         if self.nh % self.nkv:
             raise ValueError("n_heads %d is not a multiple of n_kv_heads %d" % (self.nh, self.nkv))
-        if self.hd > 256:
-            raise ValueError("head sizes up to 256 are supported, found %d" % self.hd)
+        if self.hd > 512:
+            raise ValueError("head sizes up to 512 are supported, found %d" % self.hd)
         self.window = int(spec.get("window") or 0)
         self.keep_first = int(spec.get("keep_first") or 0) if self.window else 0
         if self.keep_first < 0:
@@ -113,12 +130,22 @@ class CausalSelfAttention(Mixer):
         if rot is not None and rot[1] > self.qk_dim:
             raise ValueError("rotary_dim %d exceeds head_dim %d" % (rot[1], self.qk_dim))
         n = self._names(spec)
-        ws = [_pad_heads(weights(n["q"]), self.nh, self.qk_dim, self.hd),
-              _pad_heads(weights(n["k"]), self.nkv, self.qk_dim, self.hd),
-              _pad_heads(weights(n["v"]), self.nkv, self.v_dim, self.hd)]
+        self.shares_kv = bool(spec.get("shares_kv"))
+        if self.shares_kv and spec.get("qk_norm"):
+            raise ValueError("a layer without key and value projections cannot normalise a key projection")
+        ws = [_pad_heads(weights(n["q"]), self.nh, self.qk_dim, self.hd)]
+        if not self.shares_kv:
+            ws += [_pad_heads(weights(n["k"]), self.nkv, self.qk_dim, self.hd),
+                   _pad_heads(weights(n["v"]), self.nkv, self.v_dim, self.hd)]
+        # the gate's projection is one more block of rows of the joined product, laid out like the heads' outputs
+        self.n_main = sum(w.shape[0] for w in ws)
+        self.has_gate = bool(spec.get("gate"))
+        if self.has_gate:
+            ws.append(_pad_heads(weights(spec["gate"]), self.nh, self.v_dim, self.hd))
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v weights of %s are stored in different dtypes" % weights.prefix)
         self.wqkv = torch.cat(ws, dim=0).contiguous()
+        self.sink = weights(spec["sink"]).to(torch.float32).contiguous() if spec.get("sink") else None
         wo = weights(n["o"])
         if self.v_dim != self.hd:
             wo = _pad_heads(wo.t().contiguous(), self.nh, self.v_dim, self.hd).t().contiguous()
@@ -136,6 +163,10 @@ class CausalSelfAttention(Mixer):
         entry = ctx.entry
         reads_other = entry is not None and entry.reads_cache_of is not None
         n_q = nh * hd
+        if self.shares_kv and not reads_other:
+            raise ValueError("a layer without key and value projections must read another entry's cache")
+        if self.sink is not None or self.has_gate:
+            return self._forward_sink_gate(ctx, y, reads_other)
         if reads_other and self.qk_norm is None:
             qkv = L.rows_or_planes(ctx, y, self.wqkv[:n_q], self.dtype)
             pool, table, n_pages = ctx.cache.kv_view(entry.reads_cache_of)
@@ -159,6 +190,38 @@ class CausalSelfAttention(Mixer):
             self.position.encode_and_store(ctx, qkv, q, nh, store_kv, hd, pool, table, n_pages, qk_norm=self.qk_norm)
         A.attention(ctx, q, att, nh, nkv, hd, self.scale, self.window, pool, table, n_pages,
                     keep_first=self.keep_first)
+        return Branch(L.planes(ctx, att, self.wo))
+
+    def _forward_sink_gate(self, ctx: StepContext, y: torch.Tensor, reads_other: bool) -> Branch:
+        """the same steps for a layer with a sink in its softmax or a gate on its output: one product for
+        [q | k | v | gate] (a layer that reads another entry's cache: [q | gate]), encode and store, attention with the
+        sink, the gate inside the attention kernel where it takes one, else by a kernel of its own"""
+        nh, nkv, hd = self.nh, self.nkv, self.hd
+        entry = ctx.entry
+        n_q = nh * hd
+        if reads_other and not self.shares_kv and self.qk_norm is None:
+            # its own key and value rows are not needed: the product runs over the query and gate rows only
+            w = torch.cat([self.wqkv[:n_q], self.wqkv[self.n_main:]], dim=0) if self.has_gate else self.wqkv[:n_q]
+            if getattr(self, "_w_reads", None) is None:
+                self._w_reads = w.contiguous()
+            w, n_main = self._w_reads, n_q
+        else:
+            w, n_main = self.wqkv, self.n_main
+        qkv = L.rows_or_planes(ctx, y, w, self.dtype)
+        pool, table, n_pages = ctx.cache.kv_view(entry.reads_cache_of if reads_other else entry.cache)
+        store_kv = 0 if reads_other else nkv
+        att = torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
+        q = qkv if qkv.dim() == 2 else torch.empty((ctx.T, n_q), dtype=self.dtype, device=y.device)
+        main = qkv[..., :n_main]
+        if self.qk_norm is None:
+            self.position.encode_and_store(ctx, main, q, nh, store_kv, hd, pool, table, n_pages)
+        else:
+            self.position.encode_and_store(ctx, main, q, nh, store_kv, hd, pool, table, n_pages, qk_norm=self.qk_norm)
+        gate = qkv[..., n_main:] if self.has_gate else None
+        fused = A.attention(ctx, q, att, nh, nkv, hd, self.scale, self.window, pool, table, n_pages,
+                            keep_first=self.keep_first, sink=self.sink, gate=gate)
+        if gate is not None and not fused:
+            K.gate_mul(att, gate, att)
         return Branch(L.planes(ctx, att, self.wo))
 
     def bytes_read(self) -> int:

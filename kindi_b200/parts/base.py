@@ -78,9 +78,11 @@ class StepContext:
 @dataclass
 class Branch:
     """a branch output not yet added to the residual: ``parts`` is 32-bit ``[S, T, width]``; the sum over S, taken
-    in order, is the branch"""
+    in order, is the branch. ``scale`` (``[width]``, the norm gains' dtype; None for none): the sum is multiplied by it,
+    column by column, before it joins the residual (a model's learned per-column scale of a sub-layer's output)"""
 
     parts: torch.Tensor
+    scale: Optional[torch.Tensor] = None
 
 
 # ----------------------------------------------------------------------------- tensors by name

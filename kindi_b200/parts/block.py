@@ -4,7 +4,9 @@ The adds are deferred: each norm first adds the branch that the part before it p
 previous block's pending branch and returns its own (the reference's arrangement, ``kindi/nanbeige.py:688-718``:
 ``nbq_add_rms_q8`` adds ``br`` into ``x`` before it normalises). Which mixer, feed-forward and norms a block has is
 given by its spec; the names of the sub-prefixes of its tensors are parameters too. A block whose spec gives no
-feed-forward (``None``) is ``x += mixer(norm1(x))`` alone and has no second norm.
+feed-forward (``None``) is ``x += mixer(norm1(x))`` alone and has no second norm. ``layer_scale`` (``{"mixer": name,
+"feed_forward": name}``, names under the layer's prefix): each sub-layer's output is multiplied, column by column,
+by that tensor before the add: ``x += ls1 * mixer(norm1(x))``.
 """
 from __future__ import annotations
 
@@ -34,12 +36,21 @@ class PreNormBlock(Block):
                 if has_ff or role not in ("norm2", "feed_forward")]
 
     @classmethod
+    def _scales(cls, spec: PartSpec):
+        """{role: tensor name} of the sub-layers whose output has a learned per-column scale"""
+        has_ff = spec.get("feed_forward") is not None
+        return {role: name for role, name in (spec.get("layer_scale") or {}).items()
+                if role == "mixer" or (role == "feed_forward" and has_ff)}
+
+    @classmethod
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
         out = {}
         for role, sub in cls._roles(spec):
             ps: PartSpec = spec[role]
             for suffix, shape in part_class(_CATEGORY[role], ps.kind).tensor_shapes(ps, width).items():
                 out[sub + suffix] = shape
+        for name in cls._scales(spec).values():
+            out[name] = (width,)
         return out
 
     @classmethod
@@ -49,6 +60,8 @@ class PreNormBlock(Block):
             ps: PartSpec = spec[role]
             for suffix, kind in part_class(_CATEGORY[role], ps.kind).tensor_init(ps, width).items():
                 out[sub + suffix] = kind
+        for name in cls._scales(spec).values():
+            out[name] = "gain"
         return out
 
     @classmethod
@@ -68,6 +81,9 @@ class PreNormBlock(Block):
         self.norm2 = self.feed_forward = None
         if spec.get("feed_forward") is not None:
             self.norm2, self.feed_forward = make("norm2"), make("feed_forward")
+        scales = self._scales(spec)
+        self.scale1 = weights(scales["mixer"]) if "mixer" in scales else None
+        self.scale2 = weights(scales["feed_forward"]) if "feed_forward" in scales else None
         self.graph_safe = all(p.graph_safe for p in self._parts())
 
     def _parts(self):
@@ -76,10 +92,13 @@ class PreNormBlock(Block):
     def forward(self, ctx: StepContext, x, pending: Optional[Branch]) -> Optional[Branch]:
         y = self.norm1.add_norm(ctx, x, pending)
         pending = self.mixer.forward(ctx, y)
+        pending.scale = self.scale1
         if self.feed_forward is None:
             return pending
         y = self.norm2.add_norm(ctx, x, pending)
-        return self.feed_forward.forward(ctx, y)
+        pending = self.feed_forward.forward(ctx, y)
+        pending.scale = self.scale2
+        return pending
 
     def bytes_read(self) -> int:
         return sum(p.bytes_read() for p in self._parts())

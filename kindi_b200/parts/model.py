@@ -80,6 +80,8 @@ class DecoderModel:
         pending: Optional[Branch] = None
         for entry in self.spec.schedule:
             if entry.add_embedding:
+                if pending is not None and pending.scale is not None:
+                    raise NotImplementedError("a scaled branch cannot be pending where the embedding is added again")
                 K.residual_add(x, None if pending is None else pending.parts, x0)
                 pending = None
             ctx.entry = entry

@@ -18,24 +18,29 @@ from .base import Branch, Norm, StepContext, WeightView
 
 
 class RMSNorm(Norm):
+    """``eps`` and the gain's suffix (``weight``, default "weight") are parameters of the part"""
+
     @classmethod
     def tensor_shapes(cls, spec: PartSpec, width: int) -> Dict[str, Tuple[int, ...]]:
-        return {"weight": (width,)}
+        return {spec.get("weight", "weight"): (width,)}
 
     @classmethod
     def tensor_init(cls, spec: PartSpec, width: int) -> Dict[str, str]:
-        return {"weight": "gain"}
+        return {spec.get("weight", "weight"): "gain"}
 
     def __init__(self, spec, width, weights: WeightView, *, dtype, device):
         super().__init__(spec, width, weights, dtype=dtype, device=device)
         self.eps = float(spec["eps"])
-        self.weight = weights("weight")
+        self.weight = weights(spec.get("weight", "weight"))
 
     def add_norm(self, ctx: StepContext, x, pending: Optional[Branch], rows=None):
         n_out = x.shape[0] if rows is None else rows.numel()
         y = torch.empty((n_out, self.width), dtype=self.dtype, device=x.device)
+        scale = None if pending is None else pending.scale
+        if scale is not None and scale.dtype != self.weight.dtype:
+            scale = scale.to(self.weight.dtype)
         K.add_rmsnorm(x, None if pending is None else pending.parts, self.weight, self.eps, y, rows,
-                      write_back=rows is None and pending is not None, status=ctx.status)
+                      write_back=rows is None and pending is not None, status=ctx.status, branch_scale=scale)
         return y
 
     def bytes_read(self) -> int:
@@ -71,6 +76,8 @@ class LayerNorm(Norm):
 
     def add_norm(self, ctx: StepContext, x, pending: Optional[Branch], rows=None):
         n_out = x.shape[0] if rows is None else rows.numel()
+        if pending is not None and pending.scale is not None:
+            raise NotImplementedError("the layer norm kernel adds a branch as it is; a scaled branch needs the RMS norm")
         y = torch.empty((n_out, self.width), dtype=self.dtype, device=x.device)
         K.add_layernorm(x, None if pending is None else pending.parts, self.weight, self.bias, self.eps, y, rows,
                         write_back=rows is None and pending is not None, status=ctx.status)
