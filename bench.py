@@ -347,6 +347,79 @@ def bench_e2e(eng, batch: int, context: int, steps: int, warm: int = 48, samplin
     return (stamps[-1] - stamps[-1 - steps]) * 1000.0 / steps
 
 
+# ---------------------------------------------------------------------------------------------- --arch nilatar
+# Layer sizes that resemble real models' (random weights, four layers: windowed attention with sink and gate, latent
+# attention, linear attention with decay, windowed attention that reads the first layer's keys and values; each with
+# the gated GELU feed-forward), each beside the dense Llama-arch decoder of the same width, query/key-value heads,
+# head size, window, feed-forward size and vocabulary. The cached latent head (latent + rotated part) is 128 wide, the
+# widest the tensor-core attention kernels take.
+NILATAR_SIZES = {
+    "s": dict(width=1024, heads=8, kv=2, ff=2816, q_rank=384, lat_dim=64),
+    "m": dict(width=2048, heads=16, kv=4, ff=5632, q_rank=768, lat_dim=64),
+    "l": dict(width=4096, heads=32, kv=8, ff=11008, q_rank=1536, lat_dim=128),
+}
+NILATAR_LAYERS, NILATAR_VOCAB, NILATAR_WINDOW, NILATAR_HEAD, NILATAR_KV_RANK, NILATAR_ROT = 4, 32768, 1024, 128, 96, 32
+
+
+def nilatar_pair(sz: dict):
+    """(Nilatar config, dense Llama-arch config of equal size)"""
+    H, ff = sz["heads"], {"kind": "dense", "ff": sz["ff"]}
+    att = {"heads": H, "kv_heads": sz["kv"], "dim": NILATAR_HEAD, "vdim": NILATAR_HEAD, "scale": NILATAR_HEAD ** -0.5,
+           "mask": {"size": NILATAR_WINDOW}}
+    lat = {"heads": H, "dim": sz["lat_dim"], "rot_dim": NILATAR_ROT, "vdim": sz["lat_dim"], "q_rank": sz["q_rank"],
+           "kv_rank": NILATAR_KV_RANK, "scale": (sz["lat_dim"] + NILATAR_ROT) ** -0.5,
+           "rot": {"base": 10000.0, "dims": NILATAR_ROT,
+                   "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    lin = {"heads": H, "dim": NILATAR_HEAD, "vdim": NILATAR_HEAD,
+           "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, H - 1)) for h in range(H)]}
+    nil = {"architecture": "Nilatar", "vocab": NILATAR_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},
+           "embedding": {"scale": 1.0},
+           "layers": [{"type": "attention", "mixer": att, "mlp": ff},
+                      {"type": "latent_attention", "mixer": lat, "mlp": ff},
+                      {"type": "lightning", "mixer": lin, "mlp": ff},
+                      {"type": "attention", "mixer": dict(att, kv_from=0), "mlp": ff}]}
+    dense = dict(architectures=["LlamaForCausalLM"], model_type="llama", vocab_size=NILATAR_VOCAB,
+                 hidden_size=sz["width"], intermediate_size=sz["ff"], num_hidden_layers=NILATAR_LAYERS,
+                 num_attention_heads=H, num_key_value_heads=sz["kv"], head_dim=NILATAR_HEAD,
+                 rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False, sliding_window=NILATAR_WINDOW)
+    return nil, dense
+
+
+def bench_nilatar(a) -> int:
+    """prefill and decode throughput of the Nilatar design at three layer sizes, each beside the dense decoder of equal
+    size, with the device time per kind of launch"""
+    import torch
+    pk = peaks()
+    batch, context, tokens = a.batch, min(a.context, 4096), a.prefill_tokens
+    sizes = [x for x in (a.sizes or "s,m,l").split(",") if x in NILATAR_SIZES]
+    rows = {}
+    for name in sizes:
+        sz = NILATAR_SIZES[name]
+        nil, dense = nilatar_pair(sz)
+        ctx = batch * (context + a.steps + a.warmup + 320) + tokens + 64
+        row = {"sizes": dict(sz, layers=NILATAR_LAYERS, head=NILATAR_HEAD, window=NILATAR_WINDOW,
+                             kv_rank=NILATAR_KV_RANK, rot_dim=NILATAR_ROT)}
+        for what, cfg in (("nilatar", nil), ("dense", dense)):
+            eng = engine_from_config(cfg, ctx, batch)
+            for g in eng.cache.groups:
+                g.pool.normal_(0.0, 1.0)
+            dev_ms, _, launches, _ = bench_decode(eng, batch, context, a.steps, max(3, a.warmup), False)
+            pms = bench_prefill(eng, 3, 5, tokens)
+            kt = kernel_times(eng, batch, context, tokens)
+            row[what] = {"decode_ms": round(dev_ms, 4), "decode_tokens_per_s": round(batch * 1000.0 / dev_ms, 1),
+                         "launches_per_step": launches // a.steps, "prefill_ms": round(pms, 3),
+                         "prefill_tokens_per_s": round(tokens * 1000.0 / pms, 1),
+                         "kernels_us": {k: _grouped(v) for k, v in kt.items()}}
+            del eng
+            torch.cuda.empty_cache()
+        rows[name] = row
+    print(json.dumps({"arch": "nilatar", "what": "prefill and decode of the Nilatar design beside the dense Llama-arch "
+                      "decoder of equal size (random weights, %d layers); not the default benchmark" % NILATAR_LAYERS,
+                      "batch": batch, "context": context, "prefill_tokens": tokens, "steps": a.steps, "dtype": "bf16",
+                      "peaks": pk, "sizes": rows}))
+    return 0
+
+
 def kernel_times(eng, batch: int, context: int, prefill_tokens: int):
     """device time per kind of launch: one decode step of `batch` sequences at `context` and one prompt pass, each
     issued launch by launch (no recorded graph, launches strictly one after another) with CUDA events around every
@@ -578,10 +651,10 @@ def main(argv=None) -> int:
                          "0.7, top-p 0.8, top-k 20) and report it as e2e_sampled")
     ap.add_argument("--no-pdl", action="store_true", help="launch kernels strictly one after another")
     ap.add_argument("--prefill-only", action="store_true", help="measure only the prefill (for profiling)")
-    ap.add_argument("--arch", default="nanbeige", choices=("nanbeige", "vozinex"),
-                    help="vozinex: not the default benchmark but the Vozinex design at a few layer sizes, each beside "
+    ap.add_argument("--arch", default="nanbeige", choices=("nanbeige", "vozinex", "nilatar"),
+                    help="vozinex, nilatar: not the default benchmark but that design at a few layer sizes, each beside "
                          "the dense decoder of equal size (prefill, decode, device time per kind of launch)")
-    ap.add_argument("--sizes", default="", help="with --arch vozinex: which of s,m,l (default: all)")
+    ap.add_argument("--sizes", default="", help="with --arch vozinex or nilatar: which of s,m,l (default: all)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="prompt length of --prefill-only (the full run always measures 2048 tokens)")
     a = ap.parse_args(argv)
@@ -606,6 +679,8 @@ def main(argv=None) -> int:
         return 0
     if a.arch == "vozinex" and a.gpus == 1:
         return bench_vozinex(a)
+    if a.arch == "nilatar" and a.gpus == 1:
+        return bench_nilatar(a)
     if a.gpus != 1:
         print("kindi_b200 is a one-GPU library: bench.py measures N=1 only (asked for --gpus %d)" % a.gpus)
         return 2

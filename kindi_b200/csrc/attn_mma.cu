@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         const bf16* KB_STEP_DATA q, int ldq, bf16* __restrict__ out, int ldo, float* __restrict__ part_o,
         float* __restrict__ part_ml, const int* __restrict__ slot, const int* __restrict__ q_start,
         const int* __restrict__ kv_len, int nh, int nkv, int G, float scale_log2e, int window,
-        const int* __restrict__ table, int table_stride, int n_pages, int* status, AtRopeIn rp, int keep_first) {
+        const int* __restrict__ table, int table_stride, int n_pages, int* status, AtRopeIn rp, int keep_first,
+        const float* __restrict__ sink) {
     static_assert(!ROPE || DEC, "rotation inside the kernel: decode form only");
     constexpr int AT_STAGES = DEC ? 3 : 2;      // pages in flight (two CTAs fit an SM in both forms)
     constexpr int KT = HD / 16;                 // k-steps of Q K^T
@@ -422,6 +423,14 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
         if (!DEC) {
             // every row is whole in its warp: normalise and write
+            if (sink != nullptr) {
+                // a learned score of the head without key or value joins the denominator once, unscaled (the running
+                // sums are relative to the row's maximum, in powers of two)
+                if (ra < n_rows)
+                    l_a += exp2f(sink[hk * G + ra % G] * 1.4426950408889634f - (m_a == -INFINITY ? 0.0f : m_a));
+                if (rb < n_rows)
+                    l_b += exp2f(sink[hk * G + rb % G] * 1.4426950408889634f - (m_b == -INFINITY ? 0.0f : m_b));
+            }
             const float ia = l_a > 0.0f ? 1.0f / l_a : 0.0f, ib = l_b > 0.0f ? 1.0f / l_b : 0.0f;
             if (ra < n_rows) {
                 bf16* dst = out + (size_t)(qs0 + ra / G) * ldo + (size_t)(hk * G + ra % G) * HD + (lane & 3) * 2;
@@ -473,6 +482,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
         }
         const int h = hk * G + r;
         if (n_splits == 1) {
+            if (sink != nullptr) lv += exp2f(sink[h] * 1.4426950408889634f - U);
             out[(size_t)qs0 * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(lv > 0.0f ? ov / lv : 0.0f);
         } else {
             const size_t pi = ((size_t)b * nh + h) * n_splits + split;
@@ -488,11 +498,13 @@ __global__ void __launch_bounds__(AT_THREADS, 2) k_attn_mma(const __grid_constan
 // merge the position splits of a decode step in split order: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s
 // (kindi/nbq.cu:635-649)
 __global__ void k_attn_merge(const float* KB_STEP_DATA part_o, const float* KB_STEP_DATA part_ml, int n_splits,
-                             bf16* __restrict__ out, int ldo, const int* __restrict__ q_start, int nh, int HD) {
+                             bf16* __restrict__ out, int ldo, const int* __restrict__ q_start, int nh, int HD,
+                             const float* __restrict__ sink) {
     // blockDim = 4 * HD: group g = threadIdx.x / HD adds the splits 16 g .. 16 g + 15 for its column, then the four
     // group sums are added in group order: every sum has a fixed order
     __shared__ float sf[64], sl[64];              // at most 64 splits: each split's weight 2^(m_s - M), and its sum
     __shared__ float so[4][256];
+    __shared__ float s_sink;                      // the sink's share of the denominator, relative to M
     kb_pdl_launch();
     kb_pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
@@ -506,6 +518,7 @@ __global__ void k_attn_merge(const float* KB_STEP_DATA part_o, const float* KB_S
         sf[threadIdx.x + 32] = exp2f(m1 - U);
         sl[threadIdx.x] = threadIdx.x < n_splits ? part_ml[(base + threadIdx.x) * 2 + 1] : 0.0f;
         sl[threadIdx.x + 32] = threadIdx.x + 32 < n_splits ? part_ml[(base + threadIdx.x + 32) * 2 + 1] : 0.0f;
+        if (threadIdx.x == 0) s_sink = sink != nullptr ? exp2f(sink[h] * 1.4426950408889634f - U) : 0.0f;
     }
     const int g = threadIdx.x / HD, d = threadIdx.x % HD;
     float t[16];
@@ -521,6 +534,7 @@ __global__ void k_attn_merge(const float* KB_STEP_DATA part_o, const float* KB_S
     if (g == 0) {
         float l = 0.0f;
         for (int s = 0; s < n_splits; s++) l = fmaf(sf[s], sl[s], l);
+        l += s_sink;
         o = ((so[0][d] + so[1][d]) + so[2][d]) + so[3][d];
         out[(size_t)q_start[b] * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.0f ? o / l : 0.0f);
     }
@@ -550,7 +564,8 @@ template <int HD, bool DEC, bool ROPE = false>
 static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, float* part_o,
                        float* part_ml, const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv,
                        float scale, int window, const int* table, int table_stride, int n_pages, int grid_x,
-                       int* status, cudaStream_t st, AtRopeIn rp = AtRopeIn(), int keep_first = 0) {
+                       int* status, cudaStream_t st, AtRopeIn rp = AtRopeIn(), int keep_first = 0,
+                       const float* sink = nullptr) {
     auto kern = k_attn_mma<HD, DEC, ROPE>;
     int sm = attn_smem_bytes<HD, DEC>();
     constexpr int ALONE = 118 * 1024;   // more than half of an SM's shared memory: a CTA that asks for it has the SM to itself
@@ -566,7 +581,7 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
     dim3 grid(grid_x, nkv, B);
     kb_launch(kern, grid, AT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, slot, q_start,
                                        kv_len, nh, nkv, nh / nkv, scale * 1.4426950408889634f, window, table,
-                                       table_stride, n_pages, status, rp, keep_first);
+                                       table_stride, n_pages, status, rp, keep_first, sink);
     return (int)cudaGetLastError();
 }
 
@@ -576,7 +591,9 @@ static int launch_attn(const CUtensorMap& map, const void* q, int ldq, void* out
 extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* part_o, float* part_ml,
                            const int* slot, const int* q_start, const int* kv_len, int B, int nh, int nkv, int hd,
                            float scale, int window, void* pool, const int* table, int table_stride, int n_pages,
-                           int decode, int grid_x, int* status, cudaStream_t st, int keep_first) {
+                           int decode, int grid_x, int* status, cudaStream_t st, int keep_first, const float* sink) {
+    // sink (float [nh] or null): exp(sink[h]) joins head h's softmax denominator, once (with position splits: in the
+    // merge)
     if (B <= 0 || grid_x <= 0) return 0;
     if (window <= 0 || keep_first < 0) keep_first = 0;
     if (decode && grid_x > 64) return (int)cudaErrorInvalidValue;
@@ -588,7 +605,7 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
     if (rc) return rc;
 #define AT_GO(HD, DEC)                                                                                          \
     rc = launch_attn<HD, DEC>(map, q, ldq, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv, scale, \
-                              window, table, table_stride, n_pages, grid_x, status, st, AtRopeIn(), keep_first)
+                              window, table, table_stride, n_pages, grid_x, status, st, AtRopeIn(), keep_first, sink)
     if (hd == 128) {
         if (decode) AT_GO(128, true); else AT_GO(128, false);
     } else {
@@ -598,7 +615,7 @@ extern "C" int kb_attn_mma(const void* q, int ldq, void* out, int ldo, float* pa
     if (rc) return rc;
     if (decode && grid_x > 1) {
         dim3 grid(nh, B);
-        kb_launch(k_attn_merge, grid, 4 * hd, 0, st, part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd);
+        kb_launch(k_attn_merge, grid, 4 * hd, 0, st, part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd, sink);
         return (int)cudaGetLastError();
     }
     return 0;
@@ -636,7 +653,8 @@ extern "C" int kb_attn_decode_rope(const float* qkv, int n_planes, long long pla
     if (rc) return rc;
     if (grid_x > 1) {
         dim3 grid(nh, B);
-        kb_launch(k_attn_merge, grid, 4 * hd, 0, st, part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd);
+        kb_launch(k_attn_merge, grid, 4 * hd, 0, st, part_o, part_ml, grid_x, (bf16*)out, ldo, q_start, nh, hd,
+                  (const float*)nullptr);
         return (int)cudaGetLastError();
     }
     return 0;
@@ -692,5 +710,5 @@ extern "C" int kb_attn_decode_static(const void* q, int ldq, void* out, int ldo,
     float* part_o = base_of_device[dev];
     float* part_ml = part_o + (size_t)B * nh * n_splits * hd;
     return kb_attn_mma(q, ldq, out, ldo, part_o, part_ml, slot, q_start, kv_len, B, nh, nkv, hd, scale, window, pool,
-                       table, table_stride, n_pages, 1, n_splits, status, st, 0);
+                       table, table_stride, n_pages, 1, n_splits, status, st, 0, nullptr);
 }

@@ -87,7 +87,8 @@ template <int FT_HD>
 __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant__ CUtensorMap kvmap,
         const bf16* KB_STEP_DATA q, int ldq, bf16* __restrict__ out, int ldo, const int* __restrict__ slot,
         const int* __restrict__ q_start, const int* __restrict__ kv_len, int nkv, int G, float scale_log2e, int window,
-        const int* __restrict__ table, int table_stride, int n_pages, int* status, int keep_first) {
+        const int* __restrict__ table, int table_stride, int n_pages, int* status, int keep_first,
+        const float* __restrict__ sink, const bf16* KB_STEP_DATA gate, int ldg) {
     constexpr int FT_TILE_BYTES = 64 * FT_HD * 2, FT_STAGE_BYTES = 2 * FT_TILE_BYTES, FT_Q_BYTES = 128 * FT_HD * 2;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -396,8 +397,15 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after();
+            // a sink: a learned score of the head without key or value joins the denominator once, unscaled (the
+            // running sums are relative to the reference m_ref, in powers of two)
+            if (sink != nullptr && row_ok)
+                l += exp2f(sink[hk * G + r % G] * 1.4426950408889634f - (m_ref == -INFINITY ? 0.0f : m_ref));
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             bf16* dst = out + (size_t)(qs0 + tok0 + (row_ok ? r / G : 0)) * ldo + (size_t)(hk * G + (row_ok ? r % G : 0)) * FT_HD;
+            // an output gate: the row's outputs times the logistic function of the gate's row (laid out like out)
+            const bf16* grow = gate == nullptr ? nullptr
+                : gate + (size_t)(qs0 + tok0 + (row_ok ? r / G : 0)) * ldg + (size_t)(hk * G + (row_ok ? r % G : 0)) * FT_HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < FT_HD; c0 += 32) {
                 uint32_t ov[32];
@@ -407,10 +415,18 @@ __global__ void __launch_bounds__(FT_THREADS, 2) k_attn_tc(const __grid_constant
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t h[4];
+                        uint4 gv = make_uint4(0u, 0u, 0u, 0u);
+                        if (grow) gv = *(const uint4*)(grow + c0 + c);
+                        const __nv_bfloat162* g2 = (const __nv_bfloat162*)&gv;
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(ov[c + 2 * k]) * inv,
-                                                                     __uint_as_float(ov[c + 2 * k + 1]) * inv);
+                            float o0 = __uint_as_float(ov[c + 2 * k]) * inv, o1 = __uint_as_float(ov[c + 2 * k + 1]) * inv;
+                            if (grow) {
+                                const float2 gf = __bfloat1622float2(g2[k]);
+                                o0 = __fdividef(o0, 1.0f + __expf(-gf.x));
+                                o1 = __fdividef(o1, 1.0f + __expf(-gf.y));
+                            }
+                            __nv_bfloat162 v = __floats2bfloat162_rn(o0, o1);
                             h[k] = *(uint32_t*)&v;
                         }
                         *(uint4*)(dst + c0 + c) = make_uint4(h[0], h[1], h[2], h[3]);
@@ -432,7 +448,7 @@ template <int HD>
 static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* out, int ldo, const int* slot,
                           const int* q_start, const int* kv_len, int B, int nh, int nkv, float scale, int window,
                           const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st,
-                          int keep_first) {
+                          int keep_first, const float* sink, const void* gate, int ldg) {
     // tiles (Q and two stages of keys and values: 96 KB at head size 128) + barriers + what aligning the base to 1024
     // can cost when it is aligned to 128: two CTAs fit an SM
     const int sm = 128 * HD * 2 + FT_STAGES * 2 * 64 * HD * 2 + 256 + 768;
@@ -444,7 +460,7 @@ static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* 
     dim3 grid(nkv, grid_x, B);
     cudaError_t e = kb_launch(k_attn_tc<HD>, grid, FT_THREADS, sm, st, map, (const bf16*)q, ldq, (bf16*)out, ldo, slot,
                               q_start, kv_len, nkv, nh / nkv, scale * 1.4426950408889634f, window, table, table_stride,
-                              n_pages, status, keep_first);
+                              n_pages, status, keep_first, sink, (const bf16*)gate, ldg);
     return (int)e;
 }
 
@@ -452,8 +468,11 @@ static int launch_attn_tc(const CUtensorMap& map, const void* q, int ldq, void* 
 extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int* slot, const int* q_start,
                           const int* kv_len, int B, int nh, int nkv, int hd, float scale, int window, void* pool,
                           const int* table, int table_stride, int n_pages, int grid_x, int* status, cudaStream_t st,
-                          int keep_first) {
+                          int keep_first, const float* sink, const void* gate, int ldg) {
+    // sink (float [nh] or null): exp(sink[h]) joins head h's softmax denominator. gate (bf16 rows [T][ldg] laid out
+    // like out, 16-byte aligned rows, or null): out *= 1 / (1 + exp(-gate))
     if (B <= 0 || grid_x <= 0) return 0;
+    if (gate && ((ldg % 8) || ((uintptr_t)gate & 15))) return (int)cudaErrorInvalidValue;
     if (window <= 0 || keep_first < 0) keep_first = 0;
     if (grid_x > 65535 || B > 65535) return (int)cudaErrorInvalidValue;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || nh / nkv > 128) return (int)cudaErrorInvalidValue;
@@ -463,7 +482,7 @@ extern "C" int kb_attn_tc(const void* q, int ldq, void* out, int ldo, const int*
     if (rc) return rc;
     if (hd == 128)
         return launch_attn_tc<128>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
-                                   table_stride, n_pages, grid_x, status, st, keep_first);
+                                   table_stride, n_pages, grid_x, status, st, keep_first, sink, gate, ldg);
     return launch_attn_tc<64>(map, q, ldq, out, ldo, slot, q_start, kv_len, B, nh, nkv, scale, window, table,
-                              table_stride, n_pages, grid_x, status, st, keep_first);
+                              table_stride, n_pages, grid_x, status, st, keep_first, sink, gate, ldg);
 }

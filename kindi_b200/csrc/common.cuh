@@ -73,6 +73,14 @@ __device__ __forceinline__ float kb_act(float z, int act) {
     }
 }
 
+// the gate of a gated feed-forward (act(gate) * up) inside a product's epilogue, with the fast exponential and
+// division (their error is far below one bf16 rounding): silu(g) = g / (1 + exp(-g)), and the tanh form of GELU is
+// the same shape, gelu_tanh(g) = g / (1 + exp(-2 u)) with u = sqrt(2 / pi) (g + 0.044715 g^3)
+__device__ __forceinline__ float kb_gate_act_fast(float g, int act) {
+    const float e = act == KB_ACT_GELU_TANH ? -1.5957691216057308f * (g + 0.044715f * g * g * g) : -g;
+    return __fdividef(g, 1.0f + __expf(e));
+}
+
 #define KB_LAUNCH_RET() return (int)cudaGetLastError()
 
 // Programmatic dependent launch. Every kernel of the library begins with kb_pdl_launch() (when its grid is small,

@@ -95,7 +95,7 @@ __device__ __forceinline__ void gp_umma_commit(uint32_t bar) {
 template <int BN, int STAGES, typename TC>
 __global__ void __launch_bounds__(GP_THREADS) k_gemm_pair(const __grid_constant__ CUtensorMap mapA,
         const __grid_constant__ CUtensorMap mapW, TC* __restrict__ C, int M, int N, int K, int ldc, int* status,
-        int swiglu_ld, float* part, int* flags) {      // (shared with other CTAs of this launch: no __restrict__)
+        int swiglu_ld, float* part, int* flags, int gate_act) {      // (part, flags: shared with other CTAs of this launch: no __restrict__)
     using S = GpSmem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -301,8 +301,8 @@ __global__ void __launch_bounds__(GP_THREADS) k_gemm_pair(const __grid_constant_
                         for (int c = 0; c < 8; c++) {
                             const float g0 = __uint_as_float(gu[2 * c]), g1 = __uint_as_float(gu[2 * c + 1]);
                             __nv_bfloat162 v = __floats2bfloat162_rn(
-                                __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(gu[16 + 2 * c]),
-                                __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(gu[16 + 2 * c + 1]));
+                                kb_gate_act_fast(g0, gate_act) * __uint_as_float(gu[16 + 2 * c]),
+                                kb_gate_act_fast(g1, gate_act) * __uint_as_float(gu[16 + 2 * c + 1]));
                             h[c] = *(uint32_t*)&v;
                         }
                         bf16* dst = orow + ((q0 + c0) >> 1);
@@ -399,7 +399,7 @@ static int gp_sm_count() {
 
 template <int BN, int STAGES, typename TC>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc, int* status,
-                       cudaStream_t st, int swiglu_ld, float* part, int* flags) {
+                       cudaStream_t st, int swiglu_ld, float* part, int* flags, int gate_act) {
     using S = GpSmem<BN, STAGES>;
     auto kern = k_gemm_pair<BN, STAGES, TC>;
     static char once_tag;               // one per instantiation: the opt-in is per (device, kernel)
@@ -426,7 +426,7 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* C, in
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_kb_pdl ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, kern, ma, mw, (TC*)C, M, N, K, ldc, status, swiglu_ld, part, flags);
+    return (int)cudaLaunchKernelEx(&cfg, kern, ma, mw, (TC*)C, M, N, K, ldc, status, swiglu_ld, part, flags, gate_act);
 }
 
 // C[M][N] = A[M][K] W[N][K]^T for prompt-sized M, on pairs of SMs. cdtype: KB_F32 or KB_BF16; bn: the pair's tile width
@@ -441,13 +441,14 @@ extern "C" int kb_gemm_pair(const void* A, const void* W, void* C, int cdtype, i
     if ((K % 8) || (lda % 8) || (ldw % 8)) return (int)cudaErrorInvalidValue;
     if (cdtype != KB_F32 && cdtype != KB_BF16) return (int)cudaErrorInvalidValue;
     const int swiglu_ld = swiglu ? ldc : 0;
+    const int gate_act = swiglu == KB_ACT_GELU_TANH ? KB_ACT_GELU_TANH : KB_ACT_SILU;   // (1 and KB_ACT_SILU: silu)
     CUtensorMap ma, mw;
     int rc;
     if ((rc = kb_make_map_bf16(&ma, A, M, K, lda, GP_BM))) return rc;
     if ((rc = kb_make_map_bf16(&mw, W, N, K, ldw, bn / 2))) return rc;
 #define GP_GO(BN, ST)                                                                                        \
-    return cdtype == KB_F32 ? launch_pair<BN, ST, float>(ma, mw, C, M, N, K, ldc, status, st, swiglu_ld, part, flags) \
-                            : launch_pair<BN, ST, bf16>(ma, mw, C, M, N, K, ldc, status, st, swiglu_ld, part, flags)
+    return cdtype == KB_F32 ? launch_pair<BN, ST, float>(ma, mw, C, M, N, K, ldc, status, st, swiglu_ld, part, flags, gate_act) \
+                            : launch_pair<BN, ST, bf16>(ma, mw, C, M, N, K, ldc, status, st, swiglu_ld, part, flags, gate_act)
     switch (bn) {
         case 64: GP_GO(64, 8);
         case 128: GP_GO(128, 8);

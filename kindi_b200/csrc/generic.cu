@@ -1145,10 +1145,6 @@ extern "C" int kb_attn_generic(const void* q, int dtype, int ldq, void* out, int
 __device__ __forceinline__ float kb_gate_act(float g, int act) {
     return act == KB_ACT_GELU_TANH ? kb_act(g, KB_ACT_GELU_TANH) : g / (1.0f + expf(-g));
 }
-__device__ __forceinline__ float kb_gate_act_fast(float g, int act) {
-    const float e = act == KB_ACT_GELU_TANH ? -1.5957691216057308f * (g + 0.044715f * g * g * g) : -g;
-    return __fdividef(g, 1.0f + __expf(e));
-}
 // gu: [T][2F] = gate then up; out[t][i] = gate / (1 + exp(-gate)) * up (kindi/nbq.cu:461-467)
 template <typename TIN, typename T>
 __global__ void k_swiglu(const TIN* KB_STEP_DATA gu, int n_planes, size_t plane_stride, T* __restrict__ out, int F,

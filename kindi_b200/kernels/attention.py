@@ -13,8 +13,10 @@ def attention(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, kee
     return value says whether the kernel applied it (False: the caller still has to)"""
     if ctx.fast:
         from . import fast
-        if fast.attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first, sink):
-            return False
+        done = fast.attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first, sink,
+                                   gate)
+        if done:
+            return done == 2
     rows_gate = gate if gate is not None and gate.dim() == 2 and gate.dtype == q.dtype else None
     K.attn_generic(q, out, ctx.pos, ctx.seq, ctx.slot, nh, nkv, hd, scale, window, pool, table, n_pages, ctx.status,
                    keep_first, sink, rows_gate)

@@ -128,12 +128,13 @@ def _prefill_split(m: int, n: int, k: int):
 _PAIR_SCRATCH = {}         # device -> (partial tiles, flags): scratch of tiles that two pairs of SMs finish together
 
 
-def _prefill_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, swiglu: bool) -> None:
+def _prefill_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor, swiglu: bool,
+                     act: str = "silu") -> None:
     m, k = a.shape
     n = w.shape[0]
     kind, bn, variant = _prefill_tile(m, n, k, swiglu)
     if kind == "tc":
-        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=status, swiglu=swiglu, mt=variant)
+        K.gemm_tc(a, w, out, swap=False, bn=bn, splits=1, status=status, swiglu=swiglu, mt=variant, act=act)
         return
     part = flags = None
     if variant:
@@ -144,7 +145,7 @@ def _prefill_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status
                     torch.zeros(8 * tiles, dtype=torch.int32, device=a.device))
             _PAIR_SCRATCH[a.device] = have
         part, flags = have
-    K.gemm_pair(a, w, out, bn=bn, status=status, swiglu=swiglu, part=part, flags=flags)
+    K.gemm_pair(a, w, out, bn=bn, status=status, swiglu=swiglu, part=part, flags=flags, act=act)
 
 
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> bool:
@@ -187,11 +188,9 @@ def gemm_swiglu_rows(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor
     """out (bf16 [M, F]) = silu(g) * u for a prompt-sized step, finished inside the product's epilogue; w_grouped
     [2F, K] holds 16 gate rows then the 16 up rows of the same outputs, group after group. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
-    if act != "silu":
-        return False
     if _swiglu_in_decode_form(a) or not _tc_ok(a, w_grouped) or n % 32 or not out.is_contiguous() or (n // 2) % 8:
         return False
-    _prefill_product(a, w_grouped, out, status, True)
+    _prefill_product(a, w_grouped, out, status, True, act)
     return True
 
 
@@ -218,8 +217,6 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
     """out (bf16 [M, F]) = silu(g) * u for a decode-sized step, finished inside the product (no split-K planes, no
     SwiGLU kernel); w_grouped [2F, K] as for gemm_swiglu_rows. False: not taken"""
     m, n = a.shape[0], w_grouped.shape[0]
-    if act != "silu":
-        return False
     if not _swiglu_in_decode_form(a) or not _tc_ok(a, w_grouped) or n % 32 or out.stride(1) != 1 \
             or out.dtype != torch.bfloat16:
         return False
@@ -230,32 +227,35 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
         _SK_SCRATCH[key] = (torch.empty(tiles * bn * 128, dtype=torch.float32, device=a.device),
                             torch.zeros(tiles, dtype=torch.int32, device=a.device))
     part, flags = _SK_SCRATCH[key]
-    K.gemm_swiglu_decode(a, w_grouped, out, bn, part, flags, status)
+    K.gemm_swiglu_decode(a, w_grouped, out, bn, part, flags, status, act)
     return True
 
 
 def attention_bf16(ctx, q, out, nh, nkv, hd, scale, window, pool, table, n_pages, keep_first: int = 0,
-                   sink=None) -> bool:
-    """the tensor-core attention kernel, where it takes the shape: head size 64 or 128, bf16, aligned rows"""
-    if sink is not None:
-        return False
+                   sink=None, gate=None) -> int:
+    """the tensor-core attention kernel, where it takes the shape: head size 64 or 128, bf16, aligned rows. Returns 0
+    (not taken), 1 (done) or 2 (done, and the output gate ``gate`` was applied inside the kernel)"""
     if hd not in (64, 128) or q.dtype != torch.bfloat16 or q.stride(0) % 8 or q.data_ptr() % 16:
-        return False
+        return 0
     g = nh // nkv
     if ctx.decode and g <= 16:
         splits = decode_splits(ctx, nkv)
         K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table,
-                   n_pages, decode=True, grid_x=splits, status=ctx.status, keep_first=keep_first)
-        return True
+                   n_pages, decode=True, grid_x=splits, status=ctx.status, keep_first=keep_first, sink=sink)
+        return 1
     # (in a recording ctx.max_q is the most rows a sequence can bring: the grid then has tiles to spare, which leave)
     if g <= 128 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0:
         # prompt-sized steps: the tcgen05 kernel (S and O in tensor memory)
+        # (the gate rides in the kernel's epilogue when it came as bf16 rows the 16-byte loads can take)
+        fuse = (gate is not None and gate.dim() == 2 and gate.dtype == torch.bfloat16 and gate.stride(1) == 1
+                and gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0)
         K.attn_tc(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,
-                  grid_x=-(-ctx.max_q // (128 // g)), status=ctx.status, keep_first=keep_first)
-        return True
+                  grid_x=-(-ctx.max_q // (128 // g)), status=ctx.status, keep_first=keep_first, sink=sink,
+                  gate=gate if fuse else None)
+        return 2 if fuse else 1
     K.attn_mma(q, out, ctx.slot, ctx.q_start, ctx.kv_len, ctx.B, nh, nkv, hd, scale, window, pool, table, n_pages,
-               decode=False, grid_x=-(-ctx.max_q * g // 64), status=ctx.status, keep_first=keep_first)
-    return True
+               decode=False, grid_x=-(-ctx.max_q * g // 64), status=ctx.status, keep_first=keep_first, sink=sink)
+    return 1
 
 
 def decode_splits(ctx, nkv: int) -> int:

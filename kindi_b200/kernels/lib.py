@@ -79,15 +79,15 @@ _SIGS = {
     "kb_gemm_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                      c_void_p, c_int, c_void_p, c_void_p],
     "kb_gemm_swiglu_decode": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                              c_void_p, c_void_p, c_void_p],
+                              c_void_p, c_void_p, c_void_p, c_int],
     "kb_attn_mma": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                    c_int],
+                    c_int, c_void_p],
     "kb_attn_decode_rope": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p,
                             c_int, c_int, c_int, c_void_p, c_void_p],
     "kb_attn_tc": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int],
+                   c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int],
     "kb_sample": [c_void_p, c_longlong, c_int, c_int, c_float, c_int, c_float, c_float, c_int, c_void_p, c_void_p,
                   c_void_p],
     "kb_penalize": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_float, c_void_p],
@@ -668,7 +668,7 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, group: int = 0, act: str = "silu
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, bn: int, splits: int,
-            status: torch.Tensor, swiglu: bool = False, mt: int = 1) -> None:
+            status: torch.Tensor, swiglu: bool = False, mt: int = 1, act: str = "silu") -> None:
     """out = a[M, K] @ w[N, K]^T on the tensor cores (bf16 in, fp32 accumulate). ``out`` is [M, N] (bf16 or fp32)
     or, with K splits, fp32 [S, M, N] where S = gemm_tc_splits(K, splits). ``swiglu`` (prefill form, bn a multiple
     of 32): w holds 16 gate rows then the 16 up rows of the same outputs, group after group, and ``out`` is the bf16
@@ -688,11 +688,12 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swap: bool, 
         assert out.shape == (M, N) and splits == 1
         stride, ldc = 0, N
     _check(load().kb_gemm_tc(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, 1 if swap else 0,
-                             bn, splits, stride, _p(status), _stream(), 1 if swiglu else 0, mt), "gemm_tc")
+                             bn, splits, stride, _p(status), _stream(), GATE_ACT[act] if swiglu else 0, mt), "gemm_tc")
 
 
 def gemm_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bn: int, status: torch.Tensor,
-              swiglu: bool = False, part: Optional[torch.Tensor] = None, flags: Optional[torch.Tensor] = None) -> None:
+              swiglu: bool = False, part: Optional[torch.Tensor] = None, flags: Optional[torch.Tensor] = None,
+              act: str = "silu") -> None:
     """out = a[M, K] @ w[N, K]^T by pairs of SMs (tcgen05 with cta_group::2: a pair computes 256 rows x bn columns,
     each CTA holding half of the weight tile), bf16 in, fp32 accumulate, ``out`` [M, N] bf16 or fp32; bn 64, 128, 192
     or 256. ``swiglu``: as for gemm_tc, ``out`` is the bf16 [M, N / 2] result silu(gate) * up. With ``part`` (fp32, at
@@ -714,11 +715,11 @@ def gemm_pair(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, bn: int, s
         assert part.dtype == torch.float32 and part.numel() >= tiles * 256 * bn and part.is_contiguous()
         assert flags.dtype == torch.int32 and flags.numel() >= 8 * tiles and flags.is_contiguous()
     _check(load().kb_gemm_pair(_p(a), _p(w), _p(out), dt(out), M, N, K, a.stride(0), w.stride(0), ldc, bn, _p(status),
-                               _stream(), 1 if swiglu else 0, _p(part), _p(flags)), "gemm_pair")
+                               _stream(), GATE_ACT[act] if swiglu else 0, _p(part), _p(flags)), "gemm_pair")
 
 
 def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tensor, bn: int, part: torch.Tensor,
-                       flags: torch.Tensor, status: torch.Tensor) -> None:
+                       flags: torch.Tensor, status: torch.Tensor, act: str = "silu") -> None:
     """out (bf16 [M, F]) = silu(g) * u with [g | u] = a[M, K] @ w_grouped[2F, K]^T (16 gate rows, then the 16 up rows
     of the same outputs), for M <= bn rows, SwiGLU finished inside the product. ``part`` (float32, at least
     ceil(2F / 128) * bn * 128) and ``flags`` (int32 zeros, at least ceil(2F / 128)) are scratch that calls on one
@@ -732,7 +733,7 @@ def gemm_swiglu_decode(a: torch.Tensor, w_grouped: torch.Tensor, out: torch.Tens
     assert F % 16 == 0 and M <= bn and part.dtype == torch.float32 and part.numel() >= tiles * bn * 128
     assert flags.dtype == torch.int32 and flags.numel() >= tiles
     _check(load().kb_gemm_swiglu_decode(_p(a), _p(w_grouped), _p(out), M, F, K, a.stride(0), w_grouped.stride(0),
-                                        out.stride(0), bn, _p(part), _p(flags), _p(status), _stream()),
+                                        out.stride(0), bn, _p(part), _p(flags), _p(status), _stream(), GATE_ACT[act]),
            "gemm_swiglu_decode")
 
 
@@ -743,11 +744,14 @@ def gemm_tc_splits(K: int, wanted: int) -> int:
 
 def attn_mma(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
              scale: float, window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, decode: bool,
-             grid_x: int, status: torch.Tensor, keep_first: int = 0) -> None:
+             grid_x: int, status: torch.Tensor, keep_first: int = 0, sink: Optional[torch.Tensor] = None) -> None:
     """tensor-core attention over the cache (bf16, head size 64 or 128). decode: one row per sequence, grid_x =
     position splits; else grid_x = ceil(most rows of a sequence * (nh / nkv) / 64). ``keep_first``: with a window,
-    the sequence's first positions that stay visible"""
-    _need_cuda(q, out, pool, table)
+    the sequence's first positions that stay visible. ``sink`` (float32 [nh]): exp(sink[h]) joins head h's softmax
+    denominator"""
+    _need_cuda(q, out, pool, table, sink)
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh
     assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert pool.is_contiguous()
     part_o = part_ml = None
@@ -757,7 +761,7 @@ def attn_mma(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, 
     _check(load().kb_attn_mma(_p(q), q.stride(0), _p(out), out.stride(0), _p(part_o), _p(part_ml), _p(slot),
                               _p(q_start), _p(kv_len), B, nh, nkv, hd, float(scale), int(window), _p(pool), _p(table),
                               table.stride(0), n_pages, 1 if decode else 0, grid_x, _p(status), _stream(),
-                              int(keep_first)), "attn_mma")
+                              int(keep_first), _p(sink)), "attn_mma")
     if decode and grid_x > 1:
         add_launches(1)         # the merge of the position splits
 
@@ -786,12 +790,20 @@ def attn_decode_rope(qkv: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tenso
 
 def attn_tc(q: torch.Tensor, out: torch.Tensor, slot, q_start, kv_len, B: int, nh: int, nkv: int, hd: int,
             scale: float, window: int, pool: torch.Tensor, table: torch.Tensor, n_pages: int, *, grid_x: int,
-            status: torch.Tensor, keep_first: int = 0) -> None:
+            status: torch.Tensor, keep_first: int = 0, sink: Optional[torch.Tensor] = None,
+            gate: Optional[torch.Tensor] = None) -> None:
     """tcgen05 attention for prompt-sized steps (bf16, head size 64 or 128): grid_x = ceil(most rows of a sequence /
-    (128 // (nh / nkv))). ``keep_first``: with a window, the sequence's first positions that stay visible"""
-    _need_cuda(q, out, pool, table)
+    (128 // (nh / nkv))). ``keep_first``: with a window, the sequence's first positions that stay visible. ``sink``
+    (float32 [nh]): exp(sink[h]) joins head h's softmax denominator. ``gate`` (bf16 rows laid out like ``out``, rows
+    16-byte aligned): the output is multiplied by the logistic function of it"""
+    _need_cuda(q, out, pool, table, sink, gate)
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh
+    if gate is not None:
+        assert gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape[0] == q.shape[0]
     assert q.dtype == out.dtype == pool.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert pool.is_contiguous() and hd in (64, 128)
     _check(load().kb_attn_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(slot), _p(q_start), _p(kv_len), B, nh, nkv,
                              hd, float(scale), int(window), _p(pool), _p(table), table.stride(0), n_pages, grid_x,
-                             _p(status), _stream(), int(keep_first)), "attn_tc")
+                             _p(status), _stream(), int(keep_first), _p(sink), _p(gate),
+                             gate.stride(0) if gate is not None else 0), "attn_tc")

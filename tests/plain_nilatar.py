@@ -18,10 +18,24 @@ The feed-forward is ``W_down (gelu_tanh(W_gate y) * (W_up y))``.
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 from typing import Dict, List, Mapping, Optional, Sequence
 
 import torch
+
+
+def load_model(model_dir: str):
+    """(the JSON object of config.json, {name: tensor}) of a model folder"""
+    from safetensors.torch import load_file
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    w = {}
+    for n in sorted(os.listdir(model_dir)):
+        if n.endswith(".safetensors"):
+            w.update(load_file(os.path.join(model_dir, n)))
+    return cfg, w
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
