@@ -290,11 +290,94 @@ __global__ void __launch_bounds__(256) k_head_gemm(const TA* KB_STEP_DATA A, int
     }
 }
 
+// The same products for bf16 operands on the tensor cores (mma.sync m16n8k16, 32-bit accumulators): a block of four
+// warps takes 64 rows x 64 columns of one head, a warp 16 rows x 64 columns; K runs in blocks of 32 through shared
+// memory (rows padded to 40 elements: the fragment loads meet no bank conflicts). Needs K % 8 == 0 and 16-byte
+// aligned rows of A and W (the loads are 16 bytes wide); a sum's order depends on K only.
+__device__ __forceinline__ void mx_mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+#define HM_BM 64
+#define HM_BN 64
+#define HM_BK 32
+#define HM_LD 40
+template <typename TG>
+__global__ void __launch_bounds__(128) k_head_gemm_mma(const bf16* KB_STEP_DATA A, int lda, int ldah,
+        const bf16* __restrict__ W, bf16* __restrict__ C, int ldc, int ldch, int M, int N, int K,
+        const TG* KB_STEP_DATA gate, int n_planes, size_t plane_stride, int ldg) {
+    __shared__ __align__(16) bf16 As[HM_BM * HM_LD];
+    __shared__ __align__(16) bf16 Ws[HM_BN * HM_LD];
+    kb_pdl_launch();
+    const int h = blockIdx.z;
+    const int m0 = blockIdx.y * HM_BM, n0 = blockIdx.x * HM_BN;
+    const bf16* Ah = A + (size_t)h * ldah;
+    const bf16* Wh = W + (size_t)h * N * K;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[j][i] = 0.0f;
+    const int lr = tid >> 2, lc = (tid & 3) * 8;       // this thread's rows (lr, lr + 32) and 8-element piece of a K block
+    kb_pdl_wait();
+    for (int k0 = 0; k0 < K; k0 += HM_BK) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int r = lr + 32 * half, k = k0 + lc;
+            uint4 av = make_uint4(0u, 0u, 0u, 0u), wv = make_uint4(0u, 0u, 0u, 0u);
+            if (m0 + r < M && k < K) av = *(const uint4*)(Ah + (size_t)(m0 + r) * lda + k);
+            if (n0 + r < N && k < K) wv = *(const uint4*)(Wh + (size_t)(n0 + r) * K + k);
+            *(uint4*)(As + r * HM_LD + lc) = av;
+            *(uint4*)(Ws + r * HM_LD + lc) = wv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < HM_BK; kk += 16) {
+            uint32_t a[4];
+            const bf16* ar = As + (warp * 16 + g) * HM_LD + kk + 2 * t;
+            a[0] = *(const uint32_t*)(ar);
+            a[1] = *(const uint32_t*)(ar + 8 * HM_LD);
+            a[2] = *(const uint32_t*)(ar + 8);
+            a[3] = *(const uint32_t*)(ar + 8 * HM_LD + 8);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const bf16* wr = Ws + (j * 8 + g) * HM_LD + kk + 2 * t;
+                mx_mma_bf16(acc[j], a, *(const uint32_t*)(wr), *(const uint32_t*)(wr + 8));
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int m = m0 + warp * 16 + g + (i >> 1) * 8, n = n0 + j * 8 + 2 * t + (i & 1);
+            if (m >= M || n >= N) continue;
+            float v = acc[j][i];
+            if (gate != nullptr)
+                v *= mx_sigmoid(mx_rd<TG>(gate + (size_t)m * ldg, n_planes, plane_stride, (size_t)h * N + n));
+            C[(size_t)m * ldc + (size_t)h * ldch + n] = __float2bfloat16_rn(v);
+        }
+}
+
 extern "C" int kb_head_gemm(const void* A, int adtype, int lda, int ldah, const void* W, int wdtype, void* C, int ldc,
                             int ldch, int M, int N, int K, int H, const void* gate, int gdtype, int n_planes,
-                            long long plane_stride, int ldg, cudaStream_t st) {
+                            long long plane_stride, int ldg, cudaStream_t st, int tensor_cores) {
     if (M <= 0 || N <= 0 || H <= 0) return 0;
     if (H > 65535) return (int)cudaErrorInvalidValue;
+    if (tensor_cores && adtype == KB_BF16 && wdtype == KB_BF16 && K % 8 == 0 && lda % 8 == 0 && ldah % 8 == 0 &&
+        ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0) {
+        dim3 gm((N + HM_BN - 1) / HM_BN, (M + HM_BM - 1) / HM_BM, H);
+        if (gate == nullptr || gdtype == KB_F32)
+            kb_launch(k_head_gemm_mma<float>, gm, 128, 0, st, (const bf16*)A, lda, ldah, (const bf16*)W, (bf16*)C, ldc,
+                      ldch, M, N, K, (const float*)gate, n_planes, (size_t)plane_stride, ldg);
+        else
+            kb_launch(k_head_gemm_mma<bf16>, gm, 128, 0, st, (const bf16*)A, lda, ldah, (const bf16*)W, (bf16*)C, ldc,
+                      ldch, M, N, K, (const bf16*)gate, n_planes, (size_t)plane_stride, ldg);
+        KB_LAUNCH_RET();
+    }
     dim3 grid((N + HG_BN - 1) / HG_BN, (M + HG_BM - 1) / HG_BM, H);
 #define KB_HG(TA, TW, TG)                                                                                       \
     kb_launch(k_head_gemm<TA, TW, TG>, grid, 256, 0, st, (const TA*)A, lda, ldah, (const TW*)W, (TA*)C, ldc,    \
@@ -381,6 +464,202 @@ __global__ void __launch_bounds__(32 * DS_COLS) k_decay_scan(const TIN* KB_STEP_
             if (j < d) srow[j] = S[i];
         }
     }
+}
+
+// The same recurrence for long prompts, parallel over runs ("chunks") of C tokens. The recurrence is linear in the
+// state, so a sequence's chunks can be worked on side by side:
+//   1. every chunk but the last: its own contribution P_c = sum_j decay^(C - 1 - j) k_j v_j^T from a zero state
+//      (k_decay_chunk<.., false>; the block of chunk 0 also keeps a copy of the state the sequence came with);
+//   2. + 3. every chunk: the state before it by S_c = decay^C S_(c-1) + P_c from the copy (a short loop over the chunks
+//      before it), then the token-by-token recurrence over its own rows with the outputs; the last chunk's block
+//      stores the sequence's new state (k_decay_chunk<.., true>).
+// A warp owns DC_CW columns of the state (four independent sums in flight), a block 32 columns; the next tile of
+// tokens is fetched into registers while the current one is worked on. All arithmetic is 32-bit; the sums differ
+// from the token-by-token kernel's by rounding only (decay^C is taken by powf).
+#define DC_CW 4
+#define DC_COLS (8 * DC_CW)
+#define DC_TILE 16
+#define DC_PER_QK (DC_TILE * 32 * DS_MAX_DPL / 256)
+#define DC_PER_V (DC_TILE * DC_COLS / 256)
+template <typename TIN, bool OUT>
+__global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in, int n_planes, size_t plane_stride,
+        int ld_in, int H, int d, int dv, const float* __restrict__ decay, const int* __restrict__ q_start,
+        const int* __restrict__ slot, float* state, float* P, float* S0, float* __restrict__ out, int ldo, int C,
+        int nc_max) {
+    extern __shared__ float sm[];
+    float* qs = sm;                                   // [DC_TILE][d]
+    float* ks = qs + DC_TILE * d;                     // [DC_TILE][d]
+    float* vs = ks + DC_TILE * d;                     // [DC_TILE][DC_COLS]
+    kb_pdl_launch();
+    const int b = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e0 = blockIdx.y * DC_COLS, ew = e0 + warp * DC_CW;
+    const int r0 = q_start[b], r1 = q_start[b + 1];
+    const int nc = (r1 - r0 + C - 1) / C;
+    if (c >= nc) return;
+    const bool last = c == nc - 1;
+    const float lam = decay[h];
+    const size_t bh = (size_t)b * H + h;
+    float* srow = state + ((size_t)slot[b] * H + h) * dv * d;
+    float* s0row = S0 + bh * dv * d;
+    kb_pdl_wait();
+    float S[DC_CW][DS_MAX_DPL];
+    if (!OUT) {
+        if (c == 0) {
+            // the state the sequence came with, for the blocks of the second pass (which overwrite the slot's own)
+            for (int x = 0; x < DC_CW; x++)
+#pragma unroll
+                for (int i = 0; i < DS_MAX_DPL; i++) {
+                    const int j = lane + 32 * i;
+                    if (ew + x < dv && j < d) s0row[(size_t)(ew + x) * d + j] = srow[(size_t)(ew + x) * d + j];
+                }
+        }
+        if (last) return;
+#pragma unroll
+        for (int x = 0; x < DC_CW; x++)
+#pragma unroll
+            for (int i = 0; i < DS_MAX_DPL; i++) S[x][i] = 0.0f;
+    } else {
+        const float lamC = powf(lam, (float)C);
+#pragma unroll
+        for (int x = 0; x < DC_CW; x++)
+#pragma unroll
+            for (int i = 0; i < DS_MAX_DPL; i++) {
+                const int j = lane + 32 * i;
+                S[x][i] = (ew + x < dv && j < d) ? s0row[(size_t)(ew + x) * d + j] : 0.0f;
+            }
+        for (int cc = 0; cc < c; cc++) {
+            const float* pr = P + (bh * nc_max + cc) * dv * d;
+#pragma unroll
+            for (int x = 0; x < DC_CW; x++)
+#pragma unroll
+                for (int i = 0; i < DS_MAX_DPL; i++) {
+                    const int j = lane + 32 * i;
+                    if (ew + x < dv && j < d) S[x][i] = fmaf(lamC, S[x][i], pr[(size_t)(ew + x) * d + j]);
+                }
+        }
+    }
+    const int ra = r0 + c * C, rz = min(ra + C, r1);
+    const size_t oq = (size_t)h * d, ok = (size_t)H * d + (size_t)h * d, ov = (size_t)2 * H * d + (size_t)h * dv;
+    float rq[DC_PER_QK], rk[DC_PER_QK], rv[DC_PER_V];
+    auto fetch = [&](int t0) {
+        const int n = min(DC_TILE, rz - t0);
+#pragma unroll
+        for (int u = 0; u < DC_PER_QK; u++) {
+            const int idx = threadIdx.x + 256 * u;
+            rq[u] = rk[u] = 0.0f;
+            if (idx < n * d) {
+                const int t = idx / d, j = idx % d;
+                const TIN* src = in + (size_t)(t0 + t) * ld_in;
+                if (OUT) rq[u] = mx_silu(mx_rd<TIN>(src, n_planes, plane_stride, oq + j));
+                rk[u] = mx_silu(mx_rd<TIN>(src, n_planes, plane_stride, ok + j));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < DC_PER_V; u++) {
+            const int idx = threadIdx.x + 256 * u;
+            const int t = idx / DC_COLS, w = idx % DC_COLS;
+            rv[u] = 0.0f;
+            if (t < n && e0 + w < dv)
+                rv[u] = mx_silu(mx_rd<TIN>(in + (size_t)(t0 + t) * ld_in, n_planes, plane_stride, ov + e0 + w));
+        }
+    };
+    auto stage = [&](int t0) {
+        const int n = min(DC_TILE, rz - t0);
+#pragma unroll
+        for (int u = 0; u < DC_PER_QK; u++) {
+            const int idx = threadIdx.x + 256 * u;
+            if (idx < n * d) {
+                if (OUT) qs[idx] = rq[u];
+                ks[idx] = rk[u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < DC_PER_V; u++) vs[threadIdx.x + 256 * u] = rv[u];
+    };
+    fetch(ra);
+    for (int t0 = ra; t0 < rz; t0 += DC_TILE) {
+        stage(t0);
+        __syncthreads();
+        if (t0 + DC_TILE < rz) fetch(t0 + DC_TILE);
+        const int n = min(DC_TILE, rz - t0);
+        for (int t = 0; t < n; t++) {
+            float kk[DS_MAX_DPL], qq[DS_MAX_DPL], pp[DC_CW];
+#pragma unroll
+            for (int i = 0; i < DS_MAX_DPL; i++) {
+                const int j = lane + 32 * i;
+                kk[i] = j < d ? ks[t * d + j] : 0.0f;
+                qq[i] = (OUT && j < d) ? qs[t * d + j] : 0.0f;
+            }
+#pragma unroll
+            for (int x = 0; x < DC_CW; x++) {
+                const float vt = vs[t * DC_COLS + warp * DC_CW + x];
+                float p = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DS_MAX_DPL; i++) {
+                    if (lane + 32 * i < d) {
+                        S[x][i] = fmaf(lam, S[x][i], __fmul_rn(kk[i], vt));
+                        if (OUT) p = fmaf(S[x][i], qq[i], p);
+                    }
+                }
+                pp[x] = p;
+            }
+            if (OUT) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                    for (int x = 0; x < DC_CW; x++) pp[x] += __shfl_xor_sync(0xffffffffu, pp[x], o);
+                if (lane == 0) {
+                    float* orow = out + (size_t)(t0 + t) * ldo + (size_t)h * dv + ew;
+#pragma unroll
+                    for (int x = 0; x < DC_CW; x++)
+                        if (ew + x < dv) orow[x] = pp[x];
+                }
+            }
+        }
+        __syncthreads();
+    }
+    float* dst = OUT ? srow : P + (bh * nc_max + c) * dv * d;
+    if (!OUT || last) {
+#pragma unroll
+        for (int x = 0; x < DC_CW; x++)
+#pragma unroll
+            for (int i = 0; i < DS_MAX_DPL; i++) {
+                const int j = lane + 32 * i;
+                if (ew + x < dv && j < d) dst[(size_t)(ew + x) * d + j] = S[x][i];
+            }
+    }
+}
+
+// chunked form: C = tokens of a chunk, nc_max = the most chunks a sequence of this step can have (the longest
+// sequence's; an upper bound is fine), P (float [B][H][nc_max][dv][d]) and S0 (float [B][H][dv][d]) scratch
+extern "C" int kb_decay_chunked(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in, int B,
+                                int H, int d, int dv, const float* decay, const int* q_start, const int* slot,
+                                float* state, float* P, float* S0, float* out, int ldo, int C, int nc_max,
+                                cudaStream_t st) {
+    if (B <= 0 || H <= 0 || nc_max <= 0) return 0;
+    if (d > 32 * DS_MAX_DPL || d <= 0 || dv <= 0 || C <= 0 || nc_max > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid(B * H, (dv + DC_COLS - 1) / DC_COLS, nc_max);
+    const size_t sm = (size_t)(2 * DC_TILE * d + DC_TILE * DC_COLS) * sizeof(float);
+#define KB_DC(TIN)                                                                                                  \
+    do {                                                                                                            \
+        if (nc_max > 1)                                                                                             \
+            kb_launch(k_decay_chunk<TIN, false>, grid, 256, sm, st, (const TIN*)in, n_planes, (size_t)plane_stride, \
+                      ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);                    \
+        else {                                                                                                      \
+            dim3 g1(B * H, (dv + DC_COLS - 1) / DC_COLS, 1);                                                        \
+            kb_launch(k_decay_chunk<TIN, false>, g1, 256, sm, st, (const TIN*)in, n_planes, (size_t)plane_stride,   \
+                      ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);                    \
+        }                                                                                                           \
+        cudaError_t e = cudaGetLastError();                                                                         \
+        if (e != cudaSuccess) return (int)e;                                                                        \
+        kb_launch(k_decay_chunk<TIN, true>, grid, 256, sm, st, (const TIN*)in, n_planes, (size_t)plane_stride,      \
+                  ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);                        \
+    } while (0)
+    if (in_dtype == KB_F32) KB_DC(float);
+    else KB_DC(bf16);
+#undef KB_DC
+    KB_LAUNCH_RET();
 }
 
 extern "C" int kb_decay_scan(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in, int B,

@@ -52,7 +52,9 @@ _SIGS = {
     "kb_latent_qrope": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                         c_int, c_int, c_int, c_void_p],
     "kb_head_gemm": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                     c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p],
+                     c_int, c_void_p, c_int, c_int, c_longlong, c_int, c_void_p, c_int],
+    "kb_decay_chunked": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "kb_decay_scan": [c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "kb_add_layernorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_int,
@@ -431,9 +433,11 @@ def latent_qrope(q: torch.Tensor, dim: int, rot: int, freq: torch.Tensor, mult: 
 
 
 def head_gemm(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int,
-              gate: Optional[torch.Tensor] = None) -> None:
+              gate: Optional[torch.Tensor] = None, tensor_cores: bool = True) -> None:
     """per head h: out[t][h * out_head_stride + n] = sum_k a[t][h * a_head_stride + k] * w[h][n][k]; w [H, N, K].
-    ``gate`` (rows or 32-bit planes [.., T, H * N]): the result is multiplied by its logistic function"""
+    ``gate`` (rows or 32-bit planes [.., T, H * N]): the result is multiplied by its logistic function. bf16 operands
+    whose rows are 16-byte aligned (K, strides multiples of 8) run on the tensor cores unless ``tensor_cores`` is
+    False; everything else takes 32-bit multiply-adds in a fixed order"""
     _need_cuda(a, w, out, gate)
     H, N, Kd = w.shape
     M = a.shape[0]
@@ -444,14 +448,16 @@ def head_gemm(a: torch.Tensor, a_head_stride: int, w: torch.Tensor, out: torch.T
         assert gate.shape[-2:] == (M, H * N)
     _check(load().kb_head_gemm(_p(a), dt(a), a.stride(0), a_head_stride, _p(w), dt(w), _p(out), out.stride(0),
                                out_head_stride, M, N, Kd, H, _p(gate), dt(gate) if gate is not None else F32, n_planes,
-                               pstride, ldg, _stream()), "head_gemm")
+                               pstride, ldg, _stream(), 1 if tensor_cores else 0), "head_gemm")
 
 
 def decay_scan(a: torch.Tensor, B: int, H: int, d: int, dv: int, decay: torch.Tensor, q_start, slot,
-               state: torch.Tensor, out: torch.Tensor) -> None:
+               state: torch.Tensor, out: torch.Tensor, chunk: int = 0, max_rows: int = 0) -> None:
     """linear attention with a decay per head over the packed rows of ``B`` sequences: ``a`` rows or 32-bit planes of
     [q (H d) | k (H d) | v (H dv) | ...] (silu is applied here); ``state`` float32 [slots, H, dv, d] is read and
-    written; ``out`` float32 [T, H dv]"""
+    written; ``out`` float32 [T, H dv]. ``chunk`` > 0: the form for long prompts that works on a sequence's runs of
+    ``chunk`` tokens side by side (``max_rows``: the most rows a sequence brings, or an upper bound); its sums differ
+    from the token-by-token form's by rounding"""
     _need_cuda(a, decay, state, out)
     n_planes, pstride, ld = _planes_of(a)
     assert a.shape[-1] >= 2 * H * d + H * dv and decay.dtype == torch.float32 and decay.numel() == H
@@ -459,6 +465,14 @@ def decay_scan(a: torch.Tensor, B: int, H: int, d: int, dv: int, decay: torch.Te
     assert out.dtype == torch.float32 and out.stride(1) == 1 and out.shape[1] == H * dv
     if d > 256:
         raise KernelError("kindi_b200: linear attention supports key sizes up to 256, found %d" % d)
+    if chunk > 0:
+        nc = max(1, -(-int(max_rows) // chunk))
+        scratch = torch.empty((B * H * (nc + 1), dv, d), dtype=torch.float32, device=out.device)
+        _check(load().kb_decay_chunked(_p(a), dt(a), n_planes, pstride, ld, B, H, d, dv, _p(decay), _p(q_start),
+                                       _p(slot), _p(state), _p(scratch), _p(scratch[B * H * nc:]), _p(out),
+                                       out.stride(0), chunk, nc, _stream()), "decay_chunked")
+        add_launches(1)
+        return
     _check(load().kb_decay_scan(_p(a), dt(a), n_planes, pstride, ld, B, H, d, dv, _p(decay), _p(q_start), _p(slot),
                                 _p(state), _p(out), out.stride(0), _stream()), "decay_scan")
 

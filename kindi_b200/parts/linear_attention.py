@@ -27,6 +27,8 @@ _DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "o": "o", "norm": "
 
 
 class DecayLinearAttention(Mixer):
+    CHUNK = 64                  # tokens of a run in the form for long prompts
+
     @classmethod
     def _names(cls, spec: PartSpec):
         n = dict(_DEFAULT_NAMES)
@@ -76,7 +78,14 @@ class DecayLinearAttention(Mixer):
         a = L.rows_or_planes(ctx, y, self.w_in, self.dtype)
         # (padding rows of a recorded step belong to no sequence and are not written by the recurrence)
         o = (torch.zeros if ctx.graph else torch.empty)((ctx.T, H * dv), dtype=torch.float32, device=y.device)
-        K.decay_scan(a, ctx.B, H, d, dv, self.decay, ctx.q_start, ctx.slot, ctx.cache.state_view(ctx.entry.cache), o)
+        # prompts of the serving path: a sequence's runs of tokens side by side (32-bit sums that differ from the
+        # token-by-token kernel's by rounding); single tokens, short steps and the true 32-bit path: token by token
+        chunk = 0
+        if ctx.fast and not ctx.decode and ctx.max_q > self.CHUNK:
+            chunk = self.CHUNK if ctx.max_q <= 32 * self.CHUNK else 2 * self.CHUNK if ctx.max_q <= 128 * self.CHUNK \
+                else 4 * self.CHUNK
+        K.decay_scan(a, ctx.B, H, d, dv, self.decay, ctx.q_start, ctx.slot, ctx.cache.state_view(ctx.entry.cache), o,
+                     chunk=chunk, max_rows=ctx.max_q)
         yn = torch.empty((ctx.T, H * dv), dtype=self.dtype, device=y.device)
         K.gated_rmsnorm(o, self.g_norm, self.eps, a[..., 2 * H * d + H * dv:], yn)
         return Branch(L.planes(ctx, yn, self.w_o))

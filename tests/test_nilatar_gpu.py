@@ -24,9 +24,10 @@ import tiny_nilatar as TN
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-# (bfloat16: five to eight sub-layers of rounded activations put a row's logits up to about 2 % of the largest logit
-# away from the 64-bit ones; what the planted key or a lost state changes is five to fifty times that)
-TOL = {"float32": 3e-5, "bfloat16": 3e-2}
+# (bfloat16: with activations stored in 16 bits the typical row of these models lies 0.3 % of the largest logit away
+# from the 64-bit result and single rows up to 4 %, with the general kernels as with the tensor-core ones; what the
+# planted key changes is 17 % to 110 %. The 32-bit runs are the sharp ones.)
+TOL = {"float32": 3e-5, "bfloat16": 6e-2}
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
@@ -271,12 +272,14 @@ def test_latent_norms_rotation_and_store(K, dtype, T, q_rank, kv_rank, rot, D, p
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("M,H,N,Kd,planes", [(1, 2, 5, 7, 1), (70, 4, 20, 16, 2), (130, 8, 48, 32, 0), (9, 3, 100, 130, 1)])
+@pytest.mark.parametrize("M,H,N,Kd,planes", [(1, 2, 5, 7, 1), (70, 4, 20, 16, 2), (130, 8, 48, 32, 0), (9, 3, 100, 130, 1),
+                                             (300, 8, 96, 128, 0), (65, 5, 41, 72, 2), (8, 16, 128, 96, 1)])
 def test_products_per_head(K, dtype, M, H, N, Kd, planes):
-    """out[t][h] = W[h] a[t][h] over strided heads, with and without the gate in the epilogue"""
+    """out[t][h] = W[h] a[t][h] over strided heads, with and without the gate in the epilogue; bf16 operands with
+    aligned rows on the tensor cores, everything else by 32-bit multiply-adds"""
     g = torch.Generator().manual_seed(M + N)
     tdt = DT[dtype]
-    sa, so = Kd + 3, N + 5                               # head strides wider than the heads
+    sa, so = Kd + (8 if Kd % 8 == 0 else 3), N + 5       # head strides wider than the heads
     a = torch.randn(M, H * sa, generator=g).to(tdt)
     w = (torch.randn(H, N, Kd, generator=g) * 0.3).to(tdt)
     want = torch.einsum("thk,hnk->thn", a.double().view(M, H, sa)[..., :Kd], w.double())
@@ -289,16 +292,20 @@ def test_products_per_head(K, dtype, M, H, N, Kd, planes):
     got = out.view(M, H, so)
     assert _rel(got[..., :N], want) < (2e-5 if dtype == "float32" else 1e-2)
     assert float(got[..., N:].float().abs().max()) == 0    # nothing written between the heads
+    out2 = torch.zeros(M, H * so, dtype=tdt, device="cuda")
+    K.head_gemm(a.cuda(), sa, w.cuda(), out2, so, gate=gate.cuda() if gate is not None else None, tensor_cores=False)
+    assert _rel(out2.view(M, H, so)[..., :N], want) < (2e-5 if dtype == "float32" else 1e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("chunk", [0, 16, 64])
 @pytest.mark.parametrize("H,d,dv,lens,planes", [(2, 16, 24, [5, 1, 40], 1), (4, 32, 64, [70, 3], 3), (1, 64, 32, [33], 1),
                                                 (3, 40, 9, [1, 1, 1, 1], 2), (2, 128, 16, [19, 130], 1),
-                                                (1, 256, 8, [17], 1)])
-def test_decayed_recurrence_and_its_state(K, dtype, H, d, dv, lens, planes):
+                                                (1, 256, 8, [17], 1), (2, 128, 128, [300, 64, 65], 1)])
+def test_decayed_recurrence_and_its_state(K, dtype, H, d, dv, lens, planes, chunk):
     """S <- decay S + k v^T, o = S^T q over several sequences in one packed step, then a second step that goes on from
-    the stored state (one token for some sequences, several for others), in slots that are not in order; the gated
-    norm over the heads"""
+    the stored state (one token for some sequences, several for others), in slots that are not in order; token by
+    token (chunk 0) and with a sequence's runs of `chunk` tokens side by side; the gated norm over the heads"""
     g = torch.Generator().manual_seed(H * d + dv)
     tdt = DT[dtype]
     B = len(lens)
@@ -345,7 +352,7 @@ def test_decayed_recurrence_and_its_state(K, dtype, H, d, dv, lens, planes):
         q_start = torch.tensor([0] + list(np.cumsum(take)), dtype=torch.int32, device="cuda")
         o = torch.full((T, H * dv), float("nan"), dtype=torch.float32, device="cuda")
         K.decay_scan(src, B, H, d, dv, decay.cuda(), q_start, torch.tensor(slots, dtype=torch.int32, device="cuda"),
-                     state, o)
+                     state, o, chunk=chunk, max_rows=max(take) + (5 if chunk else 0))
         y = torch.empty(T, H * dv, dtype=tdt, device="cuda")
         K.gated_rmsnorm(o, wn.cuda(), 1e-5, src[..., 2 * H * d + H * dv:], y)
         at = 0
