@@ -14,6 +14,8 @@ __device__ __forceinline__ float mx_rd(const TIN* src, int n_planes, size_t plan
 }
 __device__ __forceinline__ float mx_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float mx_silu(float z) { return z / (1.0f + expf(-z)); }
+// (the fast exponential and division: their error is far below one bf16 rounding; the serving path's long prompts)
+__device__ __forceinline__ float mx_silu_fast(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
 
 // sum over the block's threads in a fixed order (lanes by butterfly, warps in warp order); every thread gets it
 __device__ __forceinline__ float mx_block_sum(float v, float* red) {
@@ -469,27 +471,30 @@ __global__ void __launch_bounds__(32 * DS_COLS) k_decay_scan(const TIN* KB_STEP_
 // The same recurrence for long prompts, parallel over runs ("chunks") of C tokens. The recurrence is linear in the
 // state, so a sequence's chunks can be worked on side by side:
 //   1. every chunk but the last: its own contribution P_c = sum_j decay^(C - 1 - j) k_j v_j^T from a zero state
-//      (k_decay_chunk<.., false>; the block of chunk 0 also keeps a copy of the state the sequence came with);
-//   2. + 3. every chunk: the state before it by S_c = decay^C S_(c-1) + P_c from the copy (a short loop over the chunks
-//      before it), then the token-by-token recurrence over its own rows with the outputs; the last chunk's block
-//      stores the sequence's new state (k_decay_chunk<.., true>).
+//      (k_decay_chunk<.., false, ..>; the blocks of chunk 0 also keep a copy of the state the sequence came with);
+//   2. element by element over the chunks: S_c = decay^C S_(c-1) + P_c, leaving in P[c] the state BEFORE chunk c
+//      (k_decay_prefix);
+//   3. every chunk: from the state before it, the token-by-token recurrence over its own rows with the outputs;
+//      the last chunk's blocks store the sequence's new state (k_decay_chunk<.., true, ..>).
 // A warp owns DC_CW columns of the state (four independent sums in flight), a block 32 columns; the next tile of
 // tokens is fetched into registers while the current one is worked on. All arithmetic is 32-bit; the sums differ
-// from the token-by-token kernel's by rounding only (decay^C is taken by powf).
+// from the token-by-token kernel's by rounding only (decay^C is taken by powf, silu by the fast exponential).
 #define DC_CW 4
 #define DC_COLS (8 * DC_CW)
 #define DC_TILE 16
-#define DC_PER_QK (DC_TILE * 32 * DS_MAX_DPL / 256)
 #define DC_PER_V (DC_TILE * DC_COLS / 256)
-template <typename TIN, bool OUT>
+// DPL = elements of a column a lane holds: ceil(d / 32) rounded up to 1, 2, 4 or 8
+template <typename TIN, bool OUT, int DPL>
 __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in, int n_planes, size_t plane_stride,
         int ld_in, int H, int d, int dv, const float* __restrict__ decay, const int* __restrict__ q_start,
         const int* __restrict__ slot, float* state, float* P, float* S0, float* __restrict__ out, int ldo, int C,
         int nc_max) {
     extern __shared__ float sm[];
-    float* qs = sm;                                   // [DC_TILE][d]
-    float* ks = qs + DC_TILE * d;                     // [DC_TILE][d]
-    float* vs = ks + DC_TILE * d;                     // [DC_TILE][DC_COLS]
+    float* qs = sm;                                   // [DC_TILE][32 DPL]
+    float* ks = qs + DC_TILE * 32 * DPL;              // [DC_TILE][32 DPL] (rows of the power-of-two length, zeros past d)
+    float* vs = ks + DC_TILE * 32 * DPL;              // [DC_TILE][DC_COLS]
+    constexpr int DR = 32 * DPL;                       // a staged row's length: d rounded up to a power of two
+    constexpr int DC_PER_QK = DC_TILE * DR / 256;
     kb_pdl_launch();
     const int b = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -503,13 +508,13 @@ __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in,
     float* srow = state + ((size_t)slot[b] * H + h) * dv * d;
     float* s0row = S0 + bh * dv * d;
     kb_pdl_wait();
-    float S[DC_CW][DS_MAX_DPL];
+    float S[DC_CW][DPL];
     if (!OUT) {
         if (c == 0) {
             // the state the sequence came with, for the blocks of the second pass (which overwrite the slot's own)
             for (int x = 0; x < DC_CW; x++)
 #pragma unroll
-                for (int i = 0; i < DS_MAX_DPL; i++) {
+                for (int i = 0; i < DPL; i++) {
                     const int j = lane + 32 * i;
                     if (ew + x < dv && j < d) s0row[(size_t)(ew + x) * d + j] = srow[(size_t)(ew + x) * d + j];
                 }
@@ -518,26 +523,17 @@ __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in,
 #pragma unroll
         for (int x = 0; x < DC_CW; x++)
 #pragma unroll
-            for (int i = 0; i < DS_MAX_DPL; i++) S[x][i] = 0.0f;
+            for (int i = 0; i < DPL; i++) S[x][i] = 0.0f;
     } else {
-        const float lamC = powf(lam, (float)C);
+        // the state before this chunk, as the scan kernel left it in P[c]
+        const float* pr = P + (bh * nc_max + c) * dv * d;
 #pragma unroll
         for (int x = 0; x < DC_CW; x++)
 #pragma unroll
-            for (int i = 0; i < DS_MAX_DPL; i++) {
+            for (int i = 0; i < DPL; i++) {
                 const int j = lane + 32 * i;
-                S[x][i] = (ew + x < dv && j < d) ? s0row[(size_t)(ew + x) * d + j] : 0.0f;
+                S[x][i] = (ew + x < dv && j < d) ? pr[(size_t)(ew + x) * d + j] : 0.0f;
             }
-        for (int cc = 0; cc < c; cc++) {
-            const float* pr = P + (bh * nc_max + cc) * dv * d;
-#pragma unroll
-            for (int x = 0; x < DC_CW; x++)
-#pragma unroll
-                for (int i = 0; i < DS_MAX_DPL; i++) {
-                    const int j = lane + 32 * i;
-                    if (ew + x < dv && j < d) S[x][i] = fmaf(lamC, S[x][i], pr[(size_t)(ew + x) * d + j]);
-                }
-        }
     }
     const int ra = r0 + c * C, rz = min(ra + C, r1);
     const size_t oq = (size_t)h * d, ok = (size_t)H * d + (size_t)h * d, ov = (size_t)2 * H * d + (size_t)h * dv;
@@ -547,12 +543,12 @@ __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in,
 #pragma unroll
         for (int u = 0; u < DC_PER_QK; u++) {
             const int idx = threadIdx.x + 256 * u;
+            const int t = idx / DR, j = idx % DR;
             rq[u] = rk[u] = 0.0f;
-            if (idx < n * d) {
-                const int t = idx / d, j = idx % d;
+            if (t < n && j < d) {
                 const TIN* src = in + (size_t)(t0 + t) * ld_in;
-                if (OUT) rq[u] = mx_silu(mx_rd<TIN>(src, n_planes, plane_stride, oq + j));
-                rk[u] = mx_silu(mx_rd<TIN>(src, n_planes, plane_stride, ok + j));
+                if (OUT) rq[u] = mx_silu_fast(mx_rd<TIN>(src, n_planes, plane_stride, oq + j));
+                rk[u] = mx_silu_fast(mx_rd<TIN>(src, n_planes, plane_stride, ok + j));
             }
         }
 #pragma unroll
@@ -561,18 +557,15 @@ __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in,
             const int t = idx / DC_COLS, w = idx % DC_COLS;
             rv[u] = 0.0f;
             if (t < n && e0 + w < dv)
-                rv[u] = mx_silu(mx_rd<TIN>(in + (size_t)(t0 + t) * ld_in, n_planes, plane_stride, ov + e0 + w));
+                rv[u] = mx_silu_fast(mx_rd<TIN>(in + (size_t)(t0 + t) * ld_in, n_planes, plane_stride, ov + e0 + w));
         }
     };
     auto stage = [&](int t0) {
-        const int n = min(DC_TILE, rz - t0);
 #pragma unroll
         for (int u = 0; u < DC_PER_QK; u++) {
             const int idx = threadIdx.x + 256 * u;
-            if (idx < n * d) {
-                if (OUT) qs[idx] = rq[u];
-                ks[idx] = rk[u];
-            }
+            if (OUT) qs[idx] = rq[u];
+            ks[idx] = rk[u];
         }
 #pragma unroll
         for (int u = 0; u < DC_PER_V; u++) vs[threadIdx.x + 256 * u] = rv[u];
@@ -584,19 +577,19 @@ __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in,
         if (t0 + DC_TILE < rz) fetch(t0 + DC_TILE);
         const int n = min(DC_TILE, rz - t0);
         for (int t = 0; t < n; t++) {
-            float kk[DS_MAX_DPL], qq[DS_MAX_DPL], pp[DC_CW];
+            float kk[DPL], qq[DPL], pp[DC_CW];
 #pragma unroll
-            for (int i = 0; i < DS_MAX_DPL; i++) {
+            for (int i = 0; i < DPL; i++) {
                 const int j = lane + 32 * i;
-                kk[i] = j < d ? ks[t * d + j] : 0.0f;
-                qq[i] = (OUT && j < d) ? qs[t * d + j] : 0.0f;
+                kk[i] = ks[t * DR + j];
+                qq[i] = OUT ? qs[t * DR + j] : 0.0f;
             }
 #pragma unroll
             for (int x = 0; x < DC_CW; x++) {
                 const float vt = vs[t * DC_COLS + warp * DC_CW + x];
                 float p = 0.0f;
 #pragma unroll
-                for (int i = 0; i < DS_MAX_DPL; i++) {
+                for (int i = 0; i < DPL; i++) {
                     if (lane + 32 * i < d) {
                         S[x][i] = fmaf(lam, S[x][i], __fmul_rn(kk[i], vt));
                         if (OUT) p = fmaf(S[x][i], qq[i], p);
@@ -619,12 +612,13 @@ __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in,
         }
         __syncthreads();
     }
+    (void)s0row;
     float* dst = OUT ? srow : P + (bh * nc_max + c) * dv * d;
     if (!OUT || last) {
 #pragma unroll
         for (int x = 0; x < DC_CW; x++)
 #pragma unroll
-            for (int i = 0; i < DS_MAX_DPL; i++) {
+            for (int i = 0; i < DPL; i++) {
                 const int j = lane + 32 * i;
                 if (ew + x < dv && j < d) dst[(size_t)(ew + x) * d + j] = S[x][i];
             }
@@ -633,6 +627,161 @@ __global__ void __launch_bounds__(256) k_decay_chunk(const TIN* KB_STEP_DATA in,
 
 // chunked form: C = tokens of a chunk, nc_max = the most chunks a sequence of this step can have (the longest
 // sequence's; an upper bound is fine), P (float [B][H][nc_max][dv][d]) and S0 (float [B][H][dv][d]) scratch
+// The two passes with a THREAD per column of the state (key sizes up to 128): the thread holds its column's D
+// elements in registers, so a token's output is a private sum (no exchange between lanes), k and q of a token are
+// read from shared memory as broadcasts of four, and a block's threads write 128 neighbouring outputs. About a third
+// of the instructions per token of the warp-per-column form above, which stays for larger key sizes.
+#define DK_TILE 16
+#define DK_COLS 128
+template <typename TIN, bool OUT, int D>
+__global__ void __launch_bounds__(DK_COLS) k_decay_chunk_col(const TIN* KB_STEP_DATA in, int n_planes,
+        size_t plane_stride, int ld_in, int H, int d, int dv, const float* __restrict__ decay,
+        const int* __restrict__ q_start, const int* __restrict__ slot, float* state, float* P, float* S0,
+        float* __restrict__ out, int ldo, int C, int nc_max) {
+    extern __shared__ __align__(16) float smc[];
+    float* qs = smc;                                  // [DK_TILE][D] (zeros past d)
+    float* ks = qs + DK_TILE * D;                     // [DK_TILE][D]
+    float* vs = ks + DK_TILE * D;                     // [DK_TILE][DK_COLS]
+    kb_pdl_launch();
+    const int b = blockIdx.x / H, h = blockIdx.x % H, c = blockIdx.z;
+    const int e0 = blockIdx.y * DK_COLS, e = e0 + threadIdx.x;
+    const bool live = e < dv;
+    const int r0 = q_start[b], r1 = q_start[b + 1];
+    const int nc = (r1 - r0 + C - 1) / C;
+    if (c >= nc) return;
+    const bool last = c == nc - 1;
+    const float lam = decay[h];
+    const size_t bh = (size_t)b * H + h;
+    float* srow = state + (((size_t)slot[b] * H + h) * dv + (live ? e : 0)) * d;
+    float* s0row = S0 + (bh * dv + (live ? e : 0)) * d;
+    float* prow = P + ((bh * nc_max + c) * dv + (live ? e : 0)) * d;
+    kb_pdl_wait();
+    float S[D];
+    if (!OUT) {
+        if (c == 0 && live)
+            for (int j = 0; j < d; j++) s0row[j] = srow[j];
+        if (last) return;
+#pragma unroll
+        for (int j = 0; j < D; j++) S[j] = 0.0f;
+    } else {
+#pragma unroll
+        for (int j = 0; j < D; j++) S[j] = (live && j < d) ? prow[j] : 0.0f;
+    }
+    const int ra = r0 + c * C, rz = min(ra + C, r1);
+    const size_t oq = (size_t)h * d, ok = (size_t)H * d + (size_t)h * d, ov = (size_t)2 * H * d + (size_t)h * dv;
+    // (silu(0) = 0: a zero piece past the row's end or past d stages zeros)
+    const bool vec8 = sizeof(TIN) == 2 && n_planes == 1 && d % 8 == 0 && ld_in % 8 == 0 && ((uintptr_t)in & 15) == 0;
+    for (int t0 = ra; t0 < rz; t0 += DK_TILE) {
+        const int n = min(DK_TILE, rz - t0);
+        if (vec8) {
+            // bf16 rows whose heads start on 16-byte boundaries: eight elements a load, all of a thread's loads in
+            // flight before the first is used
+            constexpr int PER = (DK_TILE * D / 8 + DK_COLS - 1) / DK_COLS;
+            uint4 rq[PER], rk[PER];
+#pragma unroll
+            for (int u = 0; u < PER; u++) {
+                const int idx = (threadIdx.x + DK_COLS * u) * 8, t = idx / D, j = idx % D;
+                rq[u] = rk[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (idx < DK_TILE * D && t < n && j < d) {
+                    const bf16* src = (const bf16*)in + (size_t)(t0 + t) * ld_in;
+                    if (OUT) rq[u] = *(const uint4*)(src + oq + j);
+                    rk[u] = *(const uint4*)(src + ok + j);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < PER; u++) {
+                const int idx = (threadIdx.x + DK_COLS * u) * 8;
+                if (idx >= DK_TILE * D) continue;
+                const __nv_bfloat162* q2 = (const __nv_bfloat162*)&rq[u];
+                const __nv_bfloat162* k2 = (const __nv_bfloat162*)&rk[u];
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const float2 kf = __bfloat1622float2(k2[w]);
+                    ks[idx + 2 * w] = mx_silu_fast(kf.x);
+                    ks[idx + 2 * w + 1] = mx_silu_fast(kf.y);
+                    if (OUT) {
+                        const float2 qf = __bfloat1622float2(q2[w]);
+                        qs[idx + 2 * w] = mx_silu_fast(qf.x);
+                        qs[idx + 2 * w + 1] = mx_silu_fast(qf.y);
+                    }
+                }
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < DK_TILE * D; idx += DK_COLS) {
+                const int t = idx / D, j = idx % D;
+                float qv = 0.0f, kv = 0.0f;
+                if (t < n && j < d) {
+                    const TIN* src = in + (size_t)(t0 + t) * ld_in;
+                    if (OUT) qv = mx_silu_fast(mx_rd<TIN>(src, n_planes, plane_stride, oq + j));
+                    kv = mx_silu_fast(mx_rd<TIN>(src, n_planes, plane_stride, ok + j));
+                }
+                if (OUT) qs[idx] = qv;
+                ks[idx] = kv;
+            }
+        }
+        for (int t = 0; t < n; t++)
+            vs[t * DK_COLS + threadIdx.x] =
+                live ? mx_silu_fast(mx_rd<TIN>(in + (size_t)(t0 + t) * ld_in, n_planes, plane_stride, ov + e)) : 0.0f;
+        __syncthreads();
+        for (int t = 0; t < n; t++) {
+            const float v = vs[t * DK_COLS + threadIdx.x];
+            float p0 = 0.0f, p1 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < D; j += 4) {
+                const float4 k4 = *(const float4*)(ks + t * D + j);
+                S[j] = fmaf(lam, S[j], __fmul_rn(k4.x, v));
+                S[j + 1] = fmaf(lam, S[j + 1], __fmul_rn(k4.y, v));
+                S[j + 2] = fmaf(lam, S[j + 2], __fmul_rn(k4.z, v));
+                S[j + 3] = fmaf(lam, S[j + 3], __fmul_rn(k4.w, v));
+                if (OUT) {
+                    const float4 q4 = *(const float4*)(qs + t * D + j);
+                    p0 = fmaf(S[j], q4.x, p0);
+                    p1 = fmaf(S[j + 1], q4.y, p1);
+                    p0 = fmaf(S[j + 2], q4.z, p0);
+                    p1 = fmaf(S[j + 3], q4.w, p1);
+                }
+            }
+            if (OUT && live) out[(size_t)(t0 + t) * ldo + (size_t)h * dv + e] = p0 + p1;
+        }
+        __syncthreads();
+    }
+    if (live && (!OUT || last)) {
+        float* dst = OUT ? srow : prow;
+#pragma unroll
+        for (int j = 0; j < D; j++)
+            if (j < d) dst[j] = S[j];
+    }
+    (void)s0row;
+}
+
+// between the two passes: P[c] (a chunk's own contribution) becomes the state BEFORE chunk c, element by element:
+// S = the state the sequence came with; for c = 0, 1, ...: (P[c], S) <- (S, decay^C S + P[c])
+__global__ void __launch_bounds__(256) k_decay_prefix(int H, int d, int dv, const float* __restrict__ decay,
+        const int* __restrict__ q_start, float* P, const float* S0, int C, int nc_max) {
+    kb_pdl_launch();
+    const int b = blockIdx.x / H, h = blockIdx.x % H;
+    const int nc = (q_start[b + 1] - q_start[b] + C - 1) / C;
+    const float lamC = powf(decay[h], (float)C);
+    const size_t bh = (size_t)b * H + h, n = (size_t)dv * d;
+    kb_pdl_wait();
+    for (size_t x = (size_t)blockIdx.y * 256 + threadIdx.x; x < n; x += (size_t)gridDim.y * 256) {
+        float S = S0[bh * n + x];
+        // (eight chunks' contributions are fetched before the first is used: the loads do not wait for one another)
+        for (int c0 = 0; c0 < nc; c0 += 8) {
+            float own[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)            // (the last chunk's contribution is never needed, nor written)
+                own[u] = c0 + u < nc - 1 ? P[(bh * nc_max + c0 + u) * n + x] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (c0 + u < nc) {
+                    P[(bh * nc_max + c0 + u) * n + x] = S;
+                    S = fmaf(lamC, S, own[u]);
+                }
+        }
+    }
+}
+
 extern "C" int kb_decay_chunked(const void* in, int in_dtype, int n_planes, long long plane_stride, int ld_in, int B,
                                 int H, int d, int dv, const float* decay, const int* q_start, const int* slot,
                                 float* state, float* P, float* S0, float* out, int ldo, int C, int nc_max,
@@ -640,24 +789,45 @@ extern "C" int kb_decay_chunked(const void* in, int in_dtype, int n_planes, long
     if (B <= 0 || H <= 0 || nc_max <= 0) return 0;
     if (d > 32 * DS_MAX_DPL || d <= 0 || dv <= 0 || C <= 0 || nc_max > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid(B * H, (dv + DC_COLS - 1) / DC_COLS, nc_max);
-    const size_t sm = (size_t)(2 * DC_TILE * d + DC_TILE * DC_COLS) * sizeof(float);
-#define KB_DC(TIN)                                                                                                  \
+    dim3 gk(B * H, (dv + DK_COLS - 1) / DK_COLS, nc_max);
+    dim3 gs(B * H, (unsigned)((dv * d + 255) / 256 < 64 ? (dv * d + 255) / 256 : 64));
+#define KB_DC2(TIN, DPL)                                                                                            \
     do {                                                                                                            \
-        if (nc_max > 1)                                                                                             \
-            kb_launch(k_decay_chunk<TIN, false>, grid, 256, sm, st, (const TIN*)in, n_planes, (size_t)plane_stride, \
-                      ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);                    \
-        else {                                                                                                      \
-            dim3 g1(B * H, (dv + DC_COLS - 1) / DC_COLS, 1);                                                        \
-            kb_launch(k_decay_chunk<TIN, false>, g1, 256, sm, st, (const TIN*)in, n_planes, (size_t)plane_stride,   \
-                      ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);                    \
-        }                                                                                                           \
+        const size_t sm = (size_t)(2 * DC_TILE * 32 * DPL + DC_TILE * DC_COLS) * sizeof(float);                     \
+        kb_launch(k_decay_chunk<TIN, false, DPL>, grid, 256, sm, st, (const TIN*)in, n_planes,                     \
+                  (size_t)plane_stride, ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);  \
         cudaError_t e = cudaGetLastError();                                                                         \
         if (e != cudaSuccess) return (int)e;                                                                        \
-        kb_launch(k_decay_chunk<TIN, true>, grid, 256, sm, st, (const TIN*)in, n_planes, (size_t)plane_stride,      \
-                  ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);                        \
+        kb_launch(k_decay_prefix, gs, 256, 0, st, H, d, dv, decay, q_start, P, (const float*)S0, C, nc_max);        \
+        e = cudaGetLastError();                                                                                     \
+        if (e != cudaSuccess) return (int)e;                                                                        \
+        kb_launch(k_decay_chunk<TIN, true, DPL>, grid, 256, sm, st, (const TIN*)in, n_planes,                      \
+                  (size_t)plane_stride, ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);  \
+    } while (0)
+#define KB_DK2(TIN, D)                                                                                              \
+    do {                                                                                                            \
+        const size_t sm = (size_t)(2 * DK_TILE * D + DK_TILE * DK_COLS) * sizeof(float);                            \
+        kb_launch(k_decay_chunk_col<TIN, false, D>, gk, DK_COLS, sm, st, (const TIN*)in, n_planes,                  \
+                  (size_t)plane_stride, ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);  \
+        cudaError_t e = cudaGetLastError();                                                                         \
+        if (e != cudaSuccess) return (int)e;                                                                        \
+        kb_launch(k_decay_prefix, gs, 256, 0, st, H, d, dv, decay, q_start, P, (const float*)S0, C, nc_max);        \
+        e = cudaGetLastError();                                                                                     \
+        if (e != cudaSuccess) return (int)e;                                                                        \
+        kb_launch(k_decay_chunk_col<TIN, true, D>, gk, DK_COLS, sm, st, (const TIN*)in, n_planes,                   \
+                  (size_t)plane_stride, ld_in, H, d, dv, decay, q_start, slot, state, P, S0, out, ldo, C, nc_max);  \
+    } while (0)
+#define KB_DC(TIN)                          \
+    do {                                    \
+        if (d <= 32) KB_DK2(TIN, 32);       \
+        else if (d <= 64) KB_DK2(TIN, 64);  \
+        else if (d <= 128) KB_DK2(TIN, 128);\
+        else KB_DC2(TIN, 8);                \
     } while (0)
     if (in_dtype == KB_F32) KB_DC(float);
     else KB_DC(bf16);
+#undef KB_DK2
+#undef KB_DC2
 #undef KB_DC
     KB_LAUNCH_RET();
 }

@@ -471,7 +471,7 @@ def decay_scan(a: torch.Tensor, B: int, H: int, d: int, dv: int, decay: torch.Te
         _check(load().kb_decay_chunked(_p(a), dt(a), n_planes, pstride, ld, B, H, d, dv, _p(decay), _p(q_start),
                                        _p(slot), _p(state), _p(scratch), _p(scratch[B * H * nc:]), _p(out),
                                        out.stride(0), chunk, nc, _stream()), "decay_chunked")
-        add_launches(1)
+        add_launches(2)
         return
     _check(load().kb_decay_scan(_p(a), dt(a), n_planes, pstride, ld, B, H, d, dv, _p(decay), _p(q_start), _p(slot),
                                 _p(state), _p(out), out.stride(0), _stream()), "decay_scan")
