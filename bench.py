@@ -369,7 +369,7 @@ def nilatar_pair(sz: dict):
     lat = {"heads": H, "dim": sz["lat_dim"], "rot_dim": NILATAR_ROT, "vdim": sz["lat_dim"], "q_rank": sz["q_rank"],
            "kv_rank": NILATAR_KV_RANK, "scale": (sz["lat_dim"] + NILATAR_ROT) ** -0.5,
            "rot": {"base": 10000.0, "dims": NILATAR_ROT,
-                   "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+                   "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     lin = {"heads": H, "dim": NILATAR_HEAD, "vdim": NILATAR_HEAD,
            "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(1, H - 1)) for h in range(H)]}
     nil = {"architecture": "Nilatar", "vocab": NILATAR_VOCAB, "width": sz["width"], "norm": {"eps": 1e-5},

@@ -106,9 +106,9 @@ def test_stretched_frequencies():
     f, m = yarn_frequencies(10000.0, 16, None)
     assert m == 1.0 and torch.allclose(f, torch.tensor([10000.0 ** (-2.0 * i / 16) for i in range(8)], dtype=torch.float64))
     sc = {"factor": 8.0, "original": 64, "fast": 4.0, "slow": 1.0}
-    f2, m2 = yarn_frequencies(50000.0, 16, sc)
-    plain, _ = yarn_frequencies(50000.0, 16, None)
-    dim_of = lambda t: 16 * math.log(64 / (2 * math.pi * t)) / (2 * math.log(50000.0))
+    f2, m2 = yarn_frequencies(40000.0, 16, sc)
+    plain, _ = yarn_frequencies(40000.0, 16, None)
+    dim_of = lambda t: 16 * math.log(64 / (2 * math.pi * t)) / (2 * math.log(40000.0))
     lo, hi = max(math.floor(dim_of(4.0)), 0), min(math.ceil(dim_of(1.0)), 15)
     assert 0 <= lo < hi < 8                                   # the ramp lies inside the pairs
     for i in range(8):

@@ -57,10 +57,10 @@ NL_A = _config(211, 64, 1e-5, 1.7, [
 #    latent head of exactly 64, stretched frequencies whose ramp lies inside the rotated pairs, a window above a page
 #    and a layer that reads it through a narrower one, a layer without a window
 NL_B = _config(300, 128, 1e-6, 0.6, [
-    _lat(8, 32, 16, 32, 64, 48, 0.15, 50000.0, (8.0, 64, 4.0, 1.0), ff=96),
+    _lat(8, 32, 16, 32, 64, 48, 0.15, 40000.0, (8.0, 64, 4.0, 1.0), ff=96),
     _att(6, 2, 64, 64, 0.125, 70, ff=96),
     _lin(4, 32, 64, [0.5, 0.9, 0.99, 1.0], ff=64),
-    _att(6, 2, 64, 64, 0.11, 40, kv_from=1),
+    _att(6, 2, 64, 64, 0.11, 44, kv_from=1),
     _att(2, 2, 64, 64, 0.125, None, ff=96)])
 # C: head size 128 with values of 64 (widened in the cache), one key/value head, a cached latent head of 128 with five
 #    query heads on it, a window of exactly a page, a width that is no power of two
