@@ -130,6 +130,7 @@ def _read_windowed(raw: Mapping[str, Any], where: str, index: int) -> NilatarWin
         mask.finish(())
         if window is not None:
             _positive(where + ".mask.size", window)
+    r.neutral("rot", (None,), "this mixer has no position encoding")
     kv_from = r.integer("kv_from", None)
     if kv_from is not None and not (0 <= kv_from < index):
         raise ConfigError("%s: kv_from must name an earlier layer, found %d" % (where, kv_from))
@@ -166,6 +167,7 @@ def _read_latent(raw: Mapping[str, Any], where: str) -> NilatarLatent:
     kv_rank = _positive(where + ".kv_rank", r.integer("kv_rank"))
     scale = _positive(where + ".scale", r.number("scale", (dim + rot_dim) ** -0.5))
     rot = _read_rotation(r.any("rot") or {}, where + ".rot", rot_dim)
+    r.neutral("mask", (None,), "latent attention sees every earlier position")
     r.finish(())
     return NilatarLatent(heads, dim, rot_dim, vdim, q_rank, kv_rank, float(scale), rot)
 
@@ -181,6 +183,8 @@ def _read_lightning(raw: Mapping[str, Any], where: str) -> NilatarLightning:
     if not isinstance(draw, (list, tuple)) or len(draw) != heads or \
             any(isinstance(x, bool) or not isinstance(x, (int, float)) for x in draw):
         raise ConfigError("%s: decay must be a list of %d numbers (one per head)" % (where, heads))
+    r.neutral("mask", (None,), "linear attention has no window")
+    r.neutral("rot", (None,), "linear attention has no position encoding")
     r.finish(())
     return NilatarLightning(heads, dim, vdim, tuple(float(x) for x in draw))
 
